@@ -1,0 +1,22 @@
+"""B200-native exact radix top-k indexer.
+
+Drop-in for the ``fast_topk_v3`` path of flash-float-jit-kernels
+(``jit_kernel/topk_indexer.py:109``): same operator signature, hand-written
+sm_100a CUDA behind a C ABI (``include/ff_topk.h``), no CPU fallback.
+"""
+from .topk_indexer import (  # noqa: F401
+    TopkArgumentError,
+    fast_topk_v3,
+    fast_topk_transform_fused,
+    fast_topk_transform_ragged_fused,
+)
+from .context_parallel import fast_topk_v3_cp, shard_bounds  # noqa: F401
+
+__all__ = [
+    "TopkArgumentError",
+    "fast_topk_v3",
+    "fast_topk_transform_fused",
+    "fast_topk_transform_ragged_fused",
+    "fast_topk_v3_cp",
+    "shard_bounds",
+]

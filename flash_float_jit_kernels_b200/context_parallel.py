@@ -1,0 +1,122 @@
+"""Context-parallel top-k: the L axis of every row is sharded over the ranks.
+
+The reference has no multi-GPU mode (its "distributed" means CTAs of one
+thread-block cluster, ``topk_indexer_radix.cu:554-973``); the semantics here
+are those of ``fast_topk_v3`` (``jit_kernel/topk_indexer.py:109``) applied to
+the unsharded row.
+
+Three steps per call, all on the current stream:
+  1. local select on the shard -> ``k`` candidates ``(value, global index)``
+     per row, in canonical order (``ff_topk_cp_local``);
+  2. all-gather of the candidate blocks (NCCL over NVLink; ``2*B*k*4`` bytes
+     per rank);
+  3. exact merge-select of the ``P*k`` candidates (``ff_topk_cp_merge``).
+
+Exactness: shards are contiguous, so the order (value desc, global index asc)
+restricted to one shard equals that shard's local order; every global winner
+is among its shard's local top-k; merging under the same total order is exact.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .topk_indexer import TopkArgumentError, _check_common, _ptr, _require, _stream_ptr, _workspace
+
+
+def shard_bounds(L: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Columns ``[start, end)`` of rank ``rank``: equal contiguous pieces of
+    ``L // world_size`` columns (rounded down to a multiple of 4 so every shard
+    starts 16-byte aligned); the last rank takes the remainder."""
+    if world_size < 1 or not (0 <= rank < world_size):
+        raise TopkArgumentError(f"bad rank {rank} for world size {world_size}")
+    base = (L // world_size) & ~3
+    if base == 0:
+        base = L // world_size
+    start = rank * base
+    end = L if rank == world_size - 1 else start + base
+    return start, end
+
+
+class ContextParallelTopk:
+    """Reusable context-parallel top-k for one (B, k) shape.
+
+    Keeps the candidate send/receive buffers so that repeated calls allocate
+    nothing.  ``group`` is a ``torch.distributed`` process group (NCCL on GPUs).
+    """
+
+    def __init__(self, B: int, topk: int, device: torch.device, group=None):
+        _require(1 <= topk <= _lib.FF_TOPK_MAX_K, f"topk must be in [1, {_lib.FF_TOPK_MAX_K}]")
+        self.B = B
+        self.k = topk
+        self.device = torch.device(device)
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        # plane 0: value bits, plane 1: global index
+        self.send = torch.empty((2, B, topk), dtype=torch.int32, device=self.device)
+        self.recv = torch.empty((self.world, 2, B, topk), dtype=torch.int32, device=self.device)
+        self.out = torch.empty((B, topk), dtype=torch.int32, device=self.device)
+
+    # -- step 1 ---------------------------------------------------------
+    def _local(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> None:
+        lib = _lib.load()
+        B, L = score_shard.size(0), score_shard.size(1)
+        ws, ws_bytes = _workspace(lib, score_shard.device, B, L, self.k)
+        with torch.cuda.device(score_shard.device):
+            rc = lib.ff_topk_cp_local(
+                score_shard.data_ptr(), score_shard.stride(0) if B > 1 else max(score_shard.stride(0), L),
+                lengths.data_ptr(), self.send[1].data_ptr(), self.send[0].data_ptr(),
+                B, L, self.k, shard_offset, _ptr(ws), ws_bytes, None, _stream_ptr(score_shard.device))
+        _lib.check(rc, "ff_topk_cp_local")
+
+    # -- step 2 ---------------------------------------------------------
+    def _exchange(self) -> None:
+        if self.world == 1:
+            self.recv[0].copy_(self.send)
+        else:
+            dist.all_gather_into_tensor(self.recv.view(-1), self.send.view(-1), group=self.group)
+
+    # -- step 3 ---------------------------------------------------------
+    def _merge(self, lengths: torch.Tensor) -> None:
+        lib = _lib.load()
+        n_cand = self.world * self.k
+        ws, ws_bytes = _workspace(lib, self.device, self.B, n_cand, self.k)
+        with torch.cuda.device(self.device):
+            rc = lib.ff_topk_cp_merge(
+                self.recv[0, 0].data_ptr(), self.recv[0, 1].data_ptr(), self.world,
+                2 * self.B * self.k, lengths.data_ptr(), self.out.data_ptr(), self.B, self.k,
+                _ptr(ws), ws_bytes, None, _stream_ptr(self.device))
+        _lib.check(rc, "ff_topk_cp_merge")
+
+    def __call__(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> torch.Tensor:
+        """``score_shard``: (B, L_local) columns ``[shard_offset, shard_offset+L_local)``
+        of the full rows; ``lengths``: (B) int32 GLOBAL row lengths (identical on
+        every rank).  Returns (B, k) int32 global indices, identical on every rank."""
+        _require(score_shard.dim() == 2 and score_shard.size(0) == self.B, "score_shard must be [B, L_local]")
+        _require(lengths.dim() == 1 and lengths.size(0) == self.B and lengths.dtype == torch.int32
+                 and lengths.is_contiguous(), "lengths must be contiguous int32 [B]")
+        _require(shard_offset >= 0, "shard_offset must be >= 0")
+        self._local(score_shard, lengths, int(shard_offset))
+        self._exchange()
+        self._merge(lengths)
+        return self.out
+
+
+def fast_topk_v3_cp(
+    score_shard: torch.Tensor,
+    lengths: torch.Tensor,
+    topk: int,
+    shard_offset: int,
+    group=None,
+    plan: Optional[ContextParallelTopk] = None,
+) -> torch.Tensor:
+    """Functional form of :class:`ContextParallelTopk` (allocates its buffers
+    per call unless ``plan`` is passed)."""
+    _check_common(score_shard, lengths, topk, None)
+    if plan is None:
+        plan = ContextParallelTopk(score_shard.size(0), topk, score_shard.device, group)
+    return plan(score_shard, lengths, shard_offset)

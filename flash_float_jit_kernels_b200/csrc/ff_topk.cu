@@ -1,0 +1,308 @@
+// C ABI and host-side launch policy of the sm_100a exact radix top-k indexer.
+// Declarations and the reference interfaces each entry point replaces are in
+// include/ff_topk.h.
+#include "../../include/ff_topk.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "ff_topk_kernel.cuh"
+
+namespace {
+
+thread_local char g_err[256] = "";
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_cluster_override{0};
+
+constexpr int kMaxDevices = 64;
+std::once_flag g_init_once[kMaxDevices];
+int g_init_rc[kMaxDevices];
+int g_max_cluster[kMaxDevices];  // largest schedulable cluster size per device
+int g_sm_count[kMaxDevices];
+
+int fail(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+int fail_cuda(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+  return static_cast<int>(e);
+}
+
+template <typename K>
+cudaError_t prepare_kernel(K kernel) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       ff::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+}
+
+template <typename K>
+int max_cluster_for(K kernel) {
+  // Largest power-of-two cluster (<= 16) of which at least one fits on the device.
+  for (int c = ff::kMaxCluster; c > 1; c >>= 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(c, 1, 1);
+    cfg.blockDim = dim3(ff::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = ff::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = c;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0) return c;
+    (void)cudaGetLastError();
+  }
+  return 1;
+}
+
+void init_device(int device) {
+  int prev = 0;
+  cudaError_t e = cudaGetDevice(&prev);
+  if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true>);
+  if (e == cudaSuccess) {
+    g_max_cluster[device] = max_cluster_for(ff::topk_cluster_kernel<false>);
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    g_sm_count[device] = sms > 0 ? sms : 148;
+  }
+  if (prev != device) (void)cudaSetDevice(prev);
+  g_init_rc[device] = static_cast<int>(e);
+}
+
+int ensure_init(int* device_out) {
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  if (device < 0 || device >= kMaxDevices) return fail(FF_ERR_BAD_SHAPE, "device ordinal out of range");
+  std::call_once(g_init_once[device], init_device, device);
+  if (g_init_rc[device] != 0)
+    return fail_cuda(static_cast<cudaError_t>(g_init_rc[device]), "ff_topk_init");
+  *device_out = device;
+  return 0;
+}
+
+int pow2_ceil(int64_t v) {
+  int p = 1;
+  while (p < v && p < (1 << 30)) p <<= 1;
+  return p;
+}
+
+// Cluster size per row.  One CTA sweeps about 16 Ki scores; the cluster grows
+// with the row up to the largest size the device can schedule.
+int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
+  (void)B;
+  (void)k;
+  int c = g_cluster_override.load();
+  if (c == 0) {
+    const char* env = getenv("FF_TOPK_CLUSTER");
+    if (env != nullptr) c = atoi(env);
+  }
+  if (c == 0) {
+    c = pow2_ceil((L_width + 16383) / 16384);
+    if (c < 1) c = 1;
+  }
+  if (c > ff::kMaxCluster) c = ff::kMaxCluster;
+  if (c > g_max_cluster[device]) c = g_max_cluster[device];
+  return c;
+}
+
+template <bool HAS_MAP>
+int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.B) * cluster, 1, 1);
+  cfg.blockDim = dim3(ff::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = ff::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP>, p);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx(topk_cluster_kernel)");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+int check_common(int32_t B, int64_t L_width, int32_t k) {
+  if (k < 1 || k > FF_TOPK_MAX_K) return fail(FF_ERR_BAD_K, "k must be in [1, 2048]");
+  if (B < 0 || L_width < 0) return fail(FF_ERR_BAD_SHAPE, "negative B or L_width");
+  if (L_width > 0x7fffffffLL) return fail(FF_ERR_TOO_LARGE, "L_width exceeds int32 indices");
+  if (static_cast<int64_t>(B) * ff::kMaxCluster > 0x7fffffffLL)
+    return fail(FF_ERR_TOO_LARGE, "B too large for one launch");
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t ff_topk_abi_version(void) { return 1; }
+
+const char* ff_last_error_string(void) { return g_err; }
+
+int64_t ff_topk_launch_count(void) { return g_launches.load(); }
+
+int ff_topk_init(int device) {
+  if (device < 0 || device >= kMaxDevices) return fail(FF_ERR_BAD_SHAPE, "device ordinal out of range");
+  std::call_once(g_init_once[device], init_device, device);
+  if (g_init_rc[device] != 0)
+    return fail_cuda(static_cast<cudaError_t>(g_init_rc[device]), "ff_topk_init");
+  return 0;
+}
+
+int ff_topk_set_cluster_override(int32_t c) {
+  if (!(c == 0 || c == 1 || c == 2 || c == 4 || c == 8 || c == 16))
+    return fail(FF_ERR_BAD_CLUSTER, "cluster override must be 0, 1, 2, 4, 8 or 16");
+  g_cluster_override.store(c);
+  return 0;
+}
+
+int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k) {
+  int device = 0;
+  if (ensure_init(&device) != 0) return -1;
+  return choose_cluster(device, B, L_width, k);
+}
+
+size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
+  (void)B;
+  (void)L_width;
+  (void)k;
+  return 0;
+}
+
+int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
+                             const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
+                             int32_t k, int32_t epilogue, const int32_t* table,
+                             int64_t table_stride, const int32_t* cu_seqlens_q,
+                             int32_t n_table_rows, const int32_t* offsets, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_common(B, L_width, k);
+  if (rc != 0) return rc;
+  if (B == 0) return 0;
+  if (scores == nullptr || lengths == nullptr || out == nullptr)
+    return fail(FF_ERR_NULL, "scores, lengths and out must not be NULL");
+  if (row_stride < 0) return fail(FF_ERR_BAD_SHAPE, "negative row_stride");
+  if ((reinterpret_cast<uintptr_t>(scores) & 3u) != 0)
+    return fail(FF_ERR_BAD_SHAPE, "scores must be 4-byte aligned");
+  if (epilogue == FF_EPILOGUE_PAGE_TABLE) {
+    if (table == nullptr) return fail(FF_ERR_NULL, "page-table epilogue needs a table");
+    if (cu_seqlens_q != nullptr && n_table_rows < 1)
+      return fail(FF_ERR_BAD_SHAPE, "prefill page-table epilogue needs n_table_rows >= 1");
+  } else if (epilogue == FF_EPILOGUE_ADD_OFFSET) {
+    if (offsets == nullptr) return fail(FF_ERR_NULL, "offset epilogue needs offsets");
+  } else if (epilogue != FF_EPILOGUE_INDEX) {
+    return fail(FF_ERR_BAD_SHAPE, "unknown epilogue");
+  }
+  int device = 0;
+  rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  ff::TopkParams p = {};
+  p.scores = scores;
+  p.row_stride = row_stride;
+  p.lengths = lengths;
+  p.row_starts = row_starts;
+  p.out_idx = out;
+  p.B = B;
+  p.k = k;
+  p.L_width = L_width;
+  p.fixed_len = -1;
+  p.epilogue = epilogue;
+  p.table = table;
+  p.table_stride = table_stride;
+  p.cu_seqlens_q = cu_seqlens_q;
+  p.n_table_rows = n_table_rows;
+  p.offsets = offsets;
+  p.status = status;
+  return launch<false>(p, choose_cluster(device, B, L_width, k), static_cast<cudaStream_t>(stream));
+}
+
+int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
+                   const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                   int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
+                   void* stream) {
+  return ff_topk_transform_launch(scores, row_stride, lengths, row_starts, out_idx, B, L_width, k,
+                                  FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, workspace,
+                                  workspace_bytes, status, stream);
+}
+
+int ff_topk_cp_local(const float* scores, int64_t row_stride, const int32_t* lengths,
+                     int32_t* cand_idx, float* cand_val, int32_t B, int64_t L_width, int32_t k,
+                     int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                     int32_t* status, void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  int rc = check_common(B, L_width, k);
+  if (rc != 0) return rc;
+  if (B == 0) return 0;
+  if (scores == nullptr || lengths == nullptr || cand_idx == nullptr || cand_val == nullptr)
+    return fail(FF_ERR_NULL, "scores, lengths, cand_idx and cand_val must not be NULL");
+  if (shard_offset < 0 || shard_offset + L_width > 0x7fffffffLL)
+    return fail(FF_ERR_TOO_LARGE, "shard_offset + L_width exceeds int32 indices");
+  if (row_stride < 0) return fail(FF_ERR_BAD_SHAPE, "negative row_stride");
+  int device = 0;
+  rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  ff::TopkParams p = {};
+  p.scores = scores;
+  p.row_stride = row_stride;
+  p.lengths = lengths;
+  p.out_idx = cand_idx;
+  p.out_val = cand_val;
+  p.B = B;
+  p.k = k;
+  p.L_width = L_width;
+  p.shard_offset = shard_offset;
+  p.fixed_len = -1;
+  p.status = status;
+  return launch<false>(p, choose_cluster(device, B, L_width, k), static_cast<cudaStream_t>(stream));
+}
+
+int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_ranks,
+                     int64_t rank_stride, const int32_t* lengths, int32_t* out_idx, int32_t B,
+                     int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
+                     void* stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  if (n_ranks < 1 || n_ranks > 1024) return fail(FF_ERR_BAD_SHAPE, "n_ranks must be in [1, 1024]");
+  const int64_t n_cand = static_cast<int64_t>(n_ranks) * k;
+  int rc = check_common(B, n_cand, k);
+  if (rc != 0) return rc;
+  if (B == 0) return 0;
+  if (cand_val == nullptr || cand_idx == nullptr || lengths == nullptr || out_idx == nullptr)
+    return fail(FF_ERR_NULL, "cand_val, cand_idx, lengths and out_idx must not be NULL");
+  if (n_ranks > 1 && rank_stride < static_cast<int64_t>(B) * k)
+    return fail(FF_ERR_BAD_SHAPE, "rank_stride < B*k");
+  int device = 0;
+  rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  ff::TopkParams p = {};
+  p.scores = cand_val;
+  p.row_stride = k;
+  p.lengths = lengths;
+  p.idx_map = cand_idx;
+  p.seg_len = k;
+  p.seg_stride = rank_stride;
+  p.out_idx = out_idx;
+  p.B = B;
+  p.k = k;
+  p.L_width = n_cand;
+  p.fixed_len = static_cast<int32_t>(n_cand);
+  p.status = status;
+  return launch<true>(p, choose_cluster(device, B, n_cand, k), static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,104 @@
+// Shared device helpers for the sm_100a exact radix top-k indexer:
+// order-preserving key map, 64-bit composite (key, ~index), block scans and
+// the kernel parameter block.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ff {
+
+constexpr int kThreads = 512;          // threads per CTA for every kernel here
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxK = 2048;            // largest supported k
+constexpr int kSortCap = 4096;         // survivors the finishing sort can take
+constexpr int kCandCap = 4096;         // per-CTA compacted threshold-bin candidates
+constexpr int kMaxBins = 4096;         // first-level digit: top 12 key bits
+constexpr int kMaxCluster = 16;
+constexpr int kNumLevels = 6;          // 12+10+10 key bits, 11+11+10 index bits
+
+// Digit layout over the 64-bit composite (key << 32 | ~index).
+__host__ __device__ constexpr int level_shift(int l) {
+  return l == 0 ? 52 : l == 1 ? 42 : l == 2 ? 32 : l == 3 ? 21 : l == 4 ? 10 : 0;
+}
+__host__ __device__ constexpr int level_bits(int l) {
+  return l == 0 ? 12 : l == 1 ? 10 : l == 2 ? 10 : l == 3 ? 11 : l == 4 ? 11 : 10;
+}
+
+// Order-preserving fp32 -> uint32 map: a > b  <=>  key(a) > key(b), with
+// -0.0 and +0.0 mapped to the same key and every NaN mapped to the top key
+// (the order torch.sort(descending=True) uses).  The reference defines the
+// same bit trick as convert_to_uint32 (topk_indexer_radix.cu:236-239) but
+// never uses it; its live key is floor(x) (topk_indexer_radix.cu:228-231).
+__host__ __device__ __forceinline__ uint32_t key_of_bits(uint32_t u) {
+  const uint32_t a = u & 0x7fffffffu;
+  if (a == 0u) u = 0u;
+  uint32_t k = u ^ (static_cast<uint32_t>(static_cast<int32_t>(u) >> 31) | 0x80000000u);
+  if (a > 0x7f800000u) k = 0xffffffffu;
+  return k;
+}
+__device__ __forceinline__ uint32_t key_of(float x) { return key_of_bits(__float_as_uint(x)); }
+
+// Inverse of key_of (up to the -0.0 / NaN canonicalisation).
+__host__ __device__ __forceinline__ uint32_t bits_of_key(uint32_t k) {
+  return (k & 0x80000000u) ? (k ^ 0x80000000u) : ~k;
+}
+
+__device__ __forceinline__ uint64_t make_comp(uint32_t key, int32_t idx) {
+  return (static_cast<uint64_t>(key) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(idx));
+}
+__device__ __forceinline__ int32_t comp_index(uint64_t c) {
+  return static_cast<int32_t>(~static_cast<uint32_t>(c));
+}
+__device__ __forceinline__ uint32_t comp_key(uint64_t c) { return static_cast<uint32_t>(c >> 32); }
+
+struct TopkParams {
+  const float* scores;         // [B, row_stride]
+  int64_t row_stride;
+  const int32_t* lengths;      // [B] (global lengths in context-parallel mode)
+  const int32_t* row_starts;   // [B] or null
+  const int32_t* idx_map;      // merge mode: explicit index per position (same addressing as scores)
+  int32_t seg_len;             // merge mode: position i lives at (i / seg_len) * seg_stride + i % seg_len
+  int64_t seg_stride;
+  int32_t* out_idx;            // [B, k]
+  float* out_val;              // [B, k] or null
+  int32_t B;
+  int32_t k;
+  int64_t L_width;
+  int64_t shard_offset;        // context-parallel: first global column of this shard
+  int32_t fixed_len;           // >= 0: every row has this many positions (merge mode)
+  int32_t epilogue;            // FF_EPILOGUE_*
+  const int32_t* table;        // page table
+  int64_t table_stride;
+  const int32_t* cu_seqlens_q; // prefill row -> request map, or null
+  int32_t n_table_rows;
+  const int32_t* offsets;      // [B] ragged offsets
+  int32_t* status;             // optional soft-error word
+};
+
+// Exclusive suffix sum over the CTA: returns the sum of `v` over all threads
+// with a higher thread index; `total` receives the CTA-wide sum.
+__device__ __forceinline__ int block_suffix_exclusive(int v, int* warp_tot, int& total) {
+  const int lane = threadIdx.x & 31;
+  const int wid = threadIdx.x >> 5;
+  int s = v;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int t = __shfl_down_sync(0xffffffffu, s, off);
+    if (lane + off < 32) s += t;
+  }
+  if (lane == 0) warp_tot[wid] = s;
+  __syncthreads();
+  int higher = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const int x = warp_tot[w];
+    tot += x;
+    if (w > wid) higher += x;
+  }
+  total = tot;
+  __syncthreads();
+  return s - v + higher;
+}
+
+}  // namespace ff

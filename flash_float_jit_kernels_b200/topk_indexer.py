@@ -1,0 +1,207 @@
+"""Python operator layer of the top-k indexer.
+
+Mirrors ``jit_kernel/topk_indexer.py:109-152`` (``fast_topk_v3``) and the
+pybind entry points ``fast_topk_transform_fused`` /
+``fast_topk_transform_ragged_fused``
+(``jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:1549-1645``) of the
+reference: same names, argument meaning and error behaviour.  PyTorch is used
+for device memory and the current stream only; all work happens in the CUDA
+library behind ``include/ff_topk.h``.
+
+Result definition: for row ``i`` the window
+``score[i, row_starts[i] : row_starts[i] + lengths[i]]`` is ranked by
+(value descending, index ascending) and the first ``topk`` window-relative
+positions are returned in that order; ``-0.0 == +0.0``; NaN ranks above
+``+inf``.  Rows with ``lengths[i] <= topk`` return ``0..lengths[i]-1`` then
+``-1`` (``topk_indexer_radix.cu:180-191``).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+
+class TopkArgumentError(AssertionError, ValueError):
+    """Bad operator arguments.
+
+    The reference signals these with ``assert`` (``topk_indexer.py:132-135``)
+    or ``TORCH_CHECK``; deriving from both lets either style of caller catch it.
+    """
+
+
+_WORKSPACES: dict = {}
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise TopkArgumentError(msg)
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream_ptr(device: torch.device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _workspace(lib, device: torch.device, B: int, L: int, k: int):
+    """Per-(device, stream) scratch, grown on demand and zero-filled once."""
+    need = int(lib.ff_topk_workspace_bytes(B, L, k))
+    if need == 0:
+        return None, 0
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws, ws.numel()
+
+
+def _check_common(score, lengths, topk, row_starts):
+    _require(isinstance(topk, int) and 1 <= topk <= _lib.FF_TOPK_MAX_K,
+             f"fast_topk_v3 supports topk in [1, {_lib.FF_TOPK_MAX_K}], got {topk}")
+    _require(score.dim() == 2, "score must be 2-D [B, L]")
+    _require(score.dtype == torch.float32, "score must be float32")
+    _require(score.is_cuda, "score must be a CUDA tensor (there is no CPU path)")
+    _require(score.size(1) == 0 or score.stride(1) == 1, "score.stride(1) must be 1")
+    B = score.size(0)
+    _require(lengths.dim() == 1 and lengths.is_contiguous() and lengths.size(0) == B,
+             "lengths must be a contiguous [B] tensor")
+    _require(lengths.dtype == torch.int32, "lengths must be int32")
+    _require(lengths.device == score.device, "lengths must live on score's device")
+    if row_starts is not None:
+        _require(row_starts.dim() == 1 and row_starts.size(0) == B and row_starts.is_contiguous(),
+                 "row_starts must be a contiguous [B] tensor")
+        _require(row_starts.dtype == torch.int32, "row_starts must be int32")
+        _require(row_starts.device == score.device, "row_starts must live on score's device")
+
+
+def fast_topk_v3(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk: int,
+    row_starts: Optional[torch.Tensor] = None,
+    *,
+    out: Optional[torch.Tensor] = None,
+    status: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Top-k indices of every row of ``score`` (reference: ``topk_indexer.py:109``).
+
+    Args:
+        score: (B, L) float32 CUDA tensor, ``stride(1) == 1``, any row stride.
+        lengths: (B) int32 valid length per row.
+        topk: number of indices per row, 1..2048 (the reference accepts
+            512, 1024 and 2048 only).
+        row_starts: optional (B) int32 window start per row; returned indices
+            are relative to the window.
+        out: optional preallocated (B, topk) int32 result (extension; lets a
+            caller keep the call allocation-free inside a CUDA graph).
+        status: optional int32 device scalar that collects soft-error bits.
+
+    Returns:
+        (B, topk) int32 indices in (value desc, index asc) order, ``-1``
+        padded for rows shorter than ``topk``.
+    """
+    _check_common(score, lengths, topk, row_starts)
+    lib = _lib.load()
+    B, L = score.size(0), score.size(1)
+    if out is None:
+        out = torch.empty((B, topk), dtype=torch.int32, device=score.device)
+    else:
+        _require(out.shape == (B, topk) and out.dtype == torch.int32 and out.is_contiguous()
+                 and out.device == score.device, "out must be a contiguous (B, topk) int32 tensor")
+    if B == 0:
+        return out
+    ws, ws_bytes = _workspace(lib, score.device, B, L, topk)
+    with torch.cuda.device(score.device):
+        rc = lib.ff_topk_launch(
+            score.data_ptr(), score.stride(0) if B > 1 else max(score.stride(0), L),
+            lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
+            _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(score.device))
+    _lib.check(rc, "fast_topk_v3")
+    return out
+
+
+def fast_topk_transform_fused(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    dst_page_table: torch.Tensor,
+    src_page_table: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    row_starts: Optional[torch.Tensor] = None,
+) -> None:
+    """Top-k followed by a page-table gather, written into ``dst_page_table``.
+
+    Mirrors ``fast_topk_transform_interface`` (``topk_indexer_radix.cu:1549-1600``):
+    ``dst[i, j] = src_page_table[r(i), idx[i, j]]`` where ``r(i) = i`` in decode
+    (``row_starts is None`` and one request per row) and otherwise the request
+    whose ``cu_seqlens_q`` interval contains row ``i``.  ``k`` is
+    ``dst_page_table.size(1)`` (the reference fixes it to 2048).
+    """
+    _require(dst_page_table.dim() == 2 and dst_page_table.is_contiguous(),
+             "dst_page_table must be contiguous 2-D")
+    topk = int(dst_page_table.size(1))
+    _check_common(score, lengths, topk, row_starts)
+    B, L = score.size(0), score.size(1)
+    _require(dst_page_table.dtype == torch.int32 and src_page_table.dtype == torch.int32,
+             "page tables must be int32")
+    _require(src_page_table.dim() == 2 and src_page_table.stride(1) == 1,
+             "src_page_table must be 2-D with unit inner stride")
+    _require(cu_seqlens_q.dim() == 1 and cu_seqlens_q.is_contiguous()
+             and cu_seqlens_q.dtype == torch.int32, "cu_seqlens_q must be contiguous int32 1-D")
+    prefill_bs = cu_seqlens_q.size(0) - 1
+    _require(dst_page_table.size(0) == B, "dst_page_table.size(0) must equal B")
+    _require(src_page_table.size(0) == prefill_bs, "src_page_table.size(0) must equal len(cu_seqlens_q)-1")
+    _require(prefill_bs <= B, "prefill batch must not exceed the expanded batch")
+    if B == 0:
+        return
+    lib = _lib.load()
+    is_decode = row_starts is None and prefill_bs == B
+    ws, ws_bytes = _workspace(lib, score.device, B, L, topk)
+    with torch.cuda.device(score.device):
+        rc = lib.ff_topk_transform_launch(
+            score.data_ptr(), score.stride(0) if B > 1 else max(score.stride(0), L),
+            lengths.data_ptr(), _ptr(row_starts), dst_page_table.data_ptr(), B, L, topk,
+            _lib.FF_EPILOGUE_PAGE_TABLE, src_page_table.data_ptr(), src_page_table.stride(0),
+            None if is_decode else cu_seqlens_q.data_ptr(), prefill_bs, None,
+            _ptr(ws), ws_bytes, None, _stream_ptr(score.device))
+    _lib.check(rc, "fast_topk_transform_fused")
+
+
+def fast_topk_transform_ragged_fused(
+    score: torch.Tensor,
+    lengths: torch.Tensor,
+    topk_indices_ragged: torch.Tensor,
+    topk_indices_offset: torch.Tensor,
+    row_starts: Optional[torch.Tensor] = None,
+) -> None:
+    """Top-k with a per-row offset added: ``out[i, j] = idx[i, j] + offset[i]``.
+
+    Mirrors ``fast_topk_transform_ragged_interface``
+    (``topk_indexer_radix.cu:1602-1639``).
+    """
+    _require(topk_indices_ragged.dim() == 2 and topk_indices_ragged.is_contiguous()
+             and topk_indices_ragged.dtype == torch.int32,
+             "topk_indices_ragged must be contiguous int32 2-D")
+    topk = int(topk_indices_ragged.size(1))
+    _check_common(score, lengths, topk, row_starts)
+    B, L = score.size(0), score.size(1)
+    _require(topk_indices_ragged.size(0) == B, "topk_indices_ragged.size(0) must equal B")
+    _require(topk_indices_offset.dim() == 1 and topk_indices_offset.size(0) == B
+             and topk_indices_offset.dtype == torch.int32 and topk_indices_offset.is_contiguous(),
+             "topk_indices_offset must be contiguous int32 [B]")
+    if B == 0:
+        return
+    lib = _lib.load()
+    ws, ws_bytes = _workspace(lib, score.device, B, L, topk)
+    with torch.cuda.device(score.device):
+        rc = lib.ff_topk_transform_launch(
+            score.data_ptr(), score.stride(0) if B > 1 else max(score.stride(0), L),
+            lengths.data_ptr(), _ptr(row_starts), topk_indices_ragged.data_ptr(), B, L, topk,
+            _lib.FF_EPILOGUE_ADD_OFFSET, None, 0, None, 0, topk_indices_offset.data_ptr(),
+            _ptr(ws), ws_bytes, None, _stream_ptr(score.device))
+    _lib.check(rc, "fast_topk_transform_ragged_fused")

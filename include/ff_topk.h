@@ -1,0 +1,142 @@
+/*
+ * ff_topk.h -- C ABI of the B200 (sm_100a) exact radix top-k indexer.
+ *
+ * Every entry point takes plain device pointers and sizes (no torch / DLPack
+ * types) so it can be bound from ctypes, cgo, JNI or a TVM-FFI shim alike.
+ * All launches are asynchronous on the caller's stream, never synchronise the
+ * host, never allocate, and never read `lengths` on the host, so a call can be
+ * captured into a CUDA graph.
+ *
+ * Selection rule (all entry points): row i is the window
+ *   scores[i*row_stride + row_starts[i] ... + lengths[i])
+ * and the result is the first k positions of that window under the total order
+ * (value descending, index ascending); -0.0 == +0.0, NaN sorts above +inf.
+ * Indices are window-relative int32.  When lengths[i] <= k the result is
+ * 0,1,...,lengths[i]-1 followed by -1 (the reference's short-row behaviour,
+ * jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:180-191).
+ *
+ * Return value: 0 on success, a negative FF_ERR_* for an argument error, a
+ * positive cudaError_t for a CUDA runtime error.  ff_last_error_string()
+ * describes the last non-zero return on the calling thread.
+ */
+#ifndef FF_TOPK_H_
+#define FF_TOPK_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FF_OK 0
+#define FF_ERR_BAD_K (-1)         /* k outside [1, FF_TOPK_MAX_K] */
+#define FF_ERR_BAD_SHAPE (-2)     /* B < 0, L_width < 0, strides inconsistent */
+#define FF_ERR_NULL (-3)          /* a required pointer is NULL */
+#define FF_ERR_WORKSPACE (-4)     /* workspace too small or misaligned */
+#define FF_ERR_BAD_CLUSTER (-5)   /* cluster-size override not in {0,1,2,4,8,16} */
+#define FF_ERR_TOO_LARGE (-6)     /* size beyond a documented maximum */
+
+#define FF_TOPK_MAX_K 2048
+
+/* Device-side soft-error bits OR-ed into the optional `status` word. */
+#define FF_STATUS_COUNT_MISMATCH 1 /* gathered survivors != histogram count   */
+#define FF_STATUS_WAIT_TIMEOUT 2   /* a bounded cross-cluster wait ran out    */
+#define FF_STATUS_NO_THRESHOLD 4   /* no threshold digit found (corrupt hist) */
+
+/* Output epilogue applied to each selected window-relative index `p`
+ * (reference: topk_indexer_radix.cu:1000-1124, the fused page-table
+ * transforms). */
+#define FF_EPILOGUE_INDEX 0       /* out = p                                  */
+#define FF_EPILOGUE_PAGE_TABLE 1  /* out = table[table_row(i)*table_stride+p] */
+#define FF_EPILOGUE_ADD_OFFSET 2  /* out = p + offsets[i]                     */
+
+/* One-time per-device set-up: kernel attributes (dynamic shared memory,
+ * non-portable 16-CTA clusters) and occupancy queries.  Idempotent and
+ * thread-safe; ff_topk_launch calls it lazily for the current device.
+ * Replaces the per-call cudaFuncSetAttribute of launch_topk_kernel
+ * (topk_indexer_radix.cu:1195-1233). */
+int ff_topk_init(int device);
+
+/* Bytes of caller-owned scratch ff_topk_launch needs for (B, L_width, k).
+ * The workspace must be 256-byte aligned, zero-filled once before first use
+ * (the kernels leave it zeroed), and must not be shared by launches that can
+ * overlap on the GPU.  May return 0 when the chosen kernel needs none. */
+size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k);
+
+/* The fast_topk_v3 hot path.  Replaces the TVM-FFI symbol `fast_topk`
+ * (topk_indexer_radix.cu:1285-1387) and the pybind `fast_topk`
+ * (topk_indexer_radix.cu:1391-1547).
+ *   scores      [B, L_width] fp32, unit inner stride, row stride `row_stride` elements
+ *   lengths     [B] int32
+ *   row_starts  [B] int32 or NULL
+ *   out_idx     [B, k] int32, contiguous; every slot is written
+ *   status      optional device int32 (NULL to ignore); soft-error bits are OR-ed in
+ *   stream      cudaStream_t
+ */
+int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
+                   const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                   int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
+                   void* stream);
+
+/* Fused top-k + page-table gather / ragged offset.  Replaces
+ * fast_topk_transform_fused and fast_topk_transform_ragged_fused
+ * (topk_indexer_radix.cu:1549-1639).
+ *   epilogue = FF_EPILOGUE_PAGE_TABLE: `table` is [n_table_rows, table_stride]
+ *     int32; row i uses table row i when cu_seqlens_q is NULL (decode), else the
+ *     request r with cu_seqlens_q[r] <= i < cu_seqlens_q[r+1] (prefill).
+ *   epilogue = FF_EPILOGUE_ADD_OFFSET: `offsets` is [B] int32.
+ */
+int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
+                             const int32_t* row_starts, int32_t* out, int32_t B,
+                             int64_t L_width, int32_t k, int32_t epilogue,
+                             const int32_t* table, int64_t table_stride,
+                             const int32_t* cu_seqlens_q, int32_t n_table_rows,
+                             const int32_t* offsets, void* workspace, size_t workspace_bytes,
+                             int32_t* status, void* stream);
+
+/* Context-parallel mode, step 1 (no reference counterpart: the reference has
+ * no multi-GPU path; semantics follow fast_topk_v3 on the unsharded row).
+ * This rank holds columns [shard_offset, shard_offset + L_width) of every row.
+ * `lengths` are the GLOBAL row lengths; the shard's valid length is
+ * clamp(lengths[i] - shard_offset, 0, L_width).  Emits the shard's top-k as
+ * (value, global index) pairs in canonical order; unused slots get
+ * (-inf, -1). */
+int ff_topk_cp_local(const float* scores, int64_t row_stride, const int32_t* lengths,
+                     int32_t* cand_idx, float* cand_val, int32_t B, int64_t L_width,
+                     int32_t k, int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                     int32_t* status, void* stream);
+
+/* Context-parallel mode, step 2: exact merge-select of the all-gathered
+ * candidates.  Rank p's block of row i is
+ *   cand_val[p*rank_stride + i*k ... + k),  cand_idx likewise
+ * (so both planes of an all-gathered [P][2][B][k] buffer can be passed with
+ * rank_stride = 2*B*k); entries with index < 0 are ignored.  `lengths` are the
+ * global row lengths (rows with lengths[i] <= k get the short-row identity
+ * result).  out_idx is [B, k] global indices in canonical order. */
+int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_ranks,
+                     int64_t rank_stride, const int32_t* lengths, int32_t* out_idx, int32_t B,
+                     int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
+                     void* stream);
+
+/* Test / tuning hook: force the thread-block-cluster size per row
+ * (0 = automatic policy, else 1, 2, 4, 8 or 16).  Process-wide. */
+int ff_topk_set_cluster_override(int32_t cluster_size);
+
+/* The cluster size the automatic policy picks for (B, L_width, k) on the
+ * current device (after overrides). */
+int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k);
+
+/* Number of kernel launches issued through this library since load
+ * (all threads); used by the benchmark's launch accounting. */
+int64_t ff_topk_launch_count(void);
+
+const char* ff_last_error_string(void);
+
+/* Library ABI version; bumped when a signature changes. */
+int32_t ff_topk_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FF_TOPK_H_ */

@@ -1,0 +1,45 @@
+"""Host-side operator checks that need no GPU: argument errors and shard arithmetic."""
+import pytest
+import torch
+
+from flash_float_jit_kernels_b200 import TopkArgumentError, fast_topk_v3, shard_bounds
+
+
+def test_cpu_tensors_are_rejected_not_silently_computed():
+    s = torch.randn(2, 64)
+    l = torch.full((2,), 64, dtype=torch.int32)
+    with pytest.raises(TopkArgumentError):
+        fast_topk_v3(s, l, 8)
+
+
+@pytest.mark.parametrize("bad_k", [0, -1, 2049, 3.5])
+def test_bad_topk_raises_like_the_reference_assert(bad_k):
+    s = torch.randn(2, 64)
+    l = torch.full((2,), 64, dtype=torch.int32)
+    with pytest.raises(AssertionError):          # reference: assert topk in (...)  topk_indexer.py:132
+        fast_topk_v3(s, l, bad_k)
+    with pytest.raises(ValueError):
+        fast_topk_v3(s, l, bad_k)
+
+
+def test_score_must_be_2d_float32():
+    l = torch.full((2,), 64, dtype=torch.int32)
+    with pytest.raises(TopkArgumentError):
+        fast_topk_v3(torch.randn(2, 4, 16), l, 8)
+    with pytest.raises(TopkArgumentError):
+        fast_topk_v3(torch.randn(2, 64).double(), l, 8)
+
+
+@pytest.mark.parametrize("L,P", [(4194304, 8), (8388608, 2), (1000003, 4), (17, 8), (5, 8), (4097, 3)])
+def test_shard_bounds_partition_the_row(L, P):
+    spans = [shard_bounds(L, P, r) for r in range(P)]
+    assert spans[0][0] == 0 and spans[-1][1] == L
+    for (a0, a1), (b0, b1) in zip(spans, spans[1:]):
+        assert a1 == b0 and a0 <= a1
+    if L >= 4 * P:
+        assert all(a % 4 == 0 for a, _ in spans)   # 16-byte aligned shard starts
+
+
+def test_shard_bounds_rejects_bad_rank():
+    with pytest.raises(TopkArgumentError):
+        shard_bounds(100, 4, 4)
