@@ -138,14 +138,6 @@ def check_selection(score_row: torch.Tensor, idx: torch.Tensor, k: int):
     assert int((score_row > thr).sum()) <= k - 1 < int((score_row >= thr).sum()), "bench: wrong selection"
 
 
-def time_graph(fn_steps, n_replays: int = 1):
-    """Captures fn_steps() into a CUDA graph; returns (graph, elapsed_ms_of_one_timed_replay_fn)."""
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        fn_steps()
-    return graph
-
-
 # ---------------------------------------------------------------------------
 # ours, one GPU
 # ---------------------------------------------------------------------------
@@ -480,6 +472,38 @@ def bench_cp(args):
     dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """A handful of eager launches of one configuration, for ncu captures (prints no bench value)."""
+    from flash_float_jit_kernels_b200 import fast_topk_v3, workloads
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    name = args.profile_case
+    n_rot = 40   # 40 x 4 MiB = 160 MiB > L2 for the 1M-column cases
+    if name == "headline":
+        rows = make_rows(n_rot, L_SHARD, dev, seed=1).view(n_rot, 1, L_SHARD)
+        lengths = torch.tensor([L_SHARD], dtype=torch.int32, device=dev)
+        k = K_TOP
+    elif name == "unique16k":
+        n_rot = 8
+        rows = torch.stack([workloads.gaussian_unique(1, 16384, seed=i, device=dev)[0] for i in range(n_rot)])
+        lengths = torch.tensor([16384], dtype=torch.int32, device=dev)
+        k = K_TOP
+    elif name == "b64":
+        n_rot = 5
+        batches = [workloads.lightning_indexer_logits(64, 131072, 4096, seed=2 + j, device=dev) for j in range(n_rot)]
+        rows = torch.stack([b[0] for b in batches])
+        lens = [b[1] for b in batches]
+        k = K_TOP
+    else:
+        raise SystemExit(f"unknown profile case {name}")
+    out = torch.empty((rows.shape[1], k), dtype=torch.int32, device=dev)
+    for i in range(max(args.warmup, 1) + args.steps):
+        l = lens[i % n_rot] if name == "b64" else lengths
+        fast_topk_v3(rows[i % n_rot], l, k, out=out)
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": name, "launches": max(args.warmup, 1) + args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -487,7 +511,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--profile-case", default=None, choices=["headline", "unique16k", "b64"],
+                    help="run a few eager launches of one configuration and exit (for ncu)")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args)
+        return
     if args.impl == "reference":
         bench_reference(args)
         return

@@ -16,6 +16,7 @@ namespace {
 thread_local char g_err[256] = "";
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_cluster_override{0};
+std::atomic<unsigned long long*> g_trace{nullptr};
 
 constexpr int kMaxDevices = 64;
 std::once_flag g_init_once[kMaxDevices];
@@ -35,7 +36,7 @@ int fail_cuda(cudaError_t e, const char* where) {
 template <typename K>
 cudaError_t prepare_kernel(K kernel) {
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       ff::kSmemBytes);
+                                       ff::smem_bytes_for(ff::kMaxStages));
   if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
 }
@@ -47,7 +48,7 @@ int max_cluster_for(K kernel) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(c, 1, 1);
     cfg.blockDim = dim3(ff::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = ff::kSmemBytes;
+    cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = c;
@@ -120,7 +121,7 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(p.B) * cluster, 1, 1);
   cfg.blockDim = dim3(ff::kThreads, 1, 1);
-  cfg.dynamicSmemBytes = ff::kSmemBytes;
+  cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -129,7 +130,10 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP>, p);
+  ff::TopkParams q = p;
+  q.trace = g_trace.load(std::memory_order_relaxed);
+  q.ring_stages = ff::kMaxStages;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP>, q);
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx(topk_cluster_kernel)");
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;
@@ -166,6 +170,11 @@ int ff_topk_set_cluster_override(int32_t c) {
   if (!(c == 0 || c == 1 || c == 2 || c == 4 || c == 8 || c == 16))
     return fail(FF_ERR_BAD_CLUSTER, "cluster override must be 0, 1, 2, 4, 8 or 16");
   g_cluster_override.store(c);
+  return 0;
+}
+
+int ff_topk_set_trace_buffer(void* device_buffer) {
+  g_trace.store(static_cast<unsigned long long*>(device_buffer));
   return 0;
 }
 

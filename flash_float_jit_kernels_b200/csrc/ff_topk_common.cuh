@@ -68,13 +68,24 @@ struct TopkParams {
   int64_t shard_offset;        // context-parallel: first global column of this shard
   int32_t fixed_len;           // >= 0: every row has this many positions (merge mode)
   int32_t epilogue;            // FF_EPILOGUE_*
+  int32_t ring_stages;         // shared-memory tiles in the streaming ring (kMinStages..kMaxStages)
   const int32_t* table;        // page table
   int64_t table_stride;
   const int32_t* cu_seqlens_q; // prefill row -> request map, or null
   int32_t n_table_rows;
   const int32_t* offsets;      // [B] ragged offsets
   int32_t* status;             // optional soft-error word
+  unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
+
+constexpr int kTraceSlots = 32;
+
+// Stage stamp for the per-CTA timeline: SM cycle counter, thread 0 only.
+#define FF_TRACE(p, slot)                                                                 \
+  do {                                                                                    \
+    if ((p).trace != nullptr && threadIdx.x == 0)                                         \
+      (p).trace[static_cast<size_t>(blockIdx.x) * ff::kTraceSlots + (slot)] = clock64();  \
+  } while (0)
 
 // Exclusive suffix sum over the CTA: returns the sum of `v` over all threads
 // with a higher thread index; `total` receives the CTA-wide sum.

@@ -1,16 +1,30 @@
 // One thread-block cluster per row: exact radix select on the 64-bit composite
-// (monotone fp32 key, ~index) followed by a finishing sort of the survivors.
+// (monotone fp32 key, ~index) followed by a counting-sort finish.
 //
 // Role in the reference: replaces topk_kernel<TopK> / fast_topk_split_kv_cuda_tl
 // (jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:554-997) and the
 // single-CTA topk_kernel_small_k (jit_kernel/csrc/topk_indexer/top_small_k.cuh:84-348).
 // Differences by design: keys are the full order-preserving 32-bit map (any
-// fp32 input, not only [0,256)); the first digit is 12 bits; per-CTA histograms
-// are merged as a reduce-scatter over distributed shared memory followed by a
+// fp32 input, not only [0,256)); the first digit is 12 bits; the CTA's chunk is
+// streamed through a ring of shared-memory tiles by bulk asynchronous copies and
+// stays resident for the second sweep when it fits; per-CTA histograms are
+// merged as a reduce-scatter over distributed shared memory followed by a
 // cluster-wide suffix scan over unequal slices; nothing is ever dropped (a CTA
 // whose threshold-bin candidates do not fit its buffer re-sweeps its chunk
 // instead); ties are broken toward the lowest index by continuing the radix
 // select into the index bits; the output is in canonical order.
+//
+// Stages per row (S = cluster barrier; plain CTA barriers when the cluster is 1 CTA):
+//   sweep 1   12-bit histogram of the CTA's chunk, tiles arriving by cp.async.bulk
+//   S  merge  each CTA sums its slice of bins from every peer's histogram (DSMEM loads)
+//      scan   suffix scan of the slice; slice totals to every peer (DSMEM stores)
+//   S  find   the CTA whose slice holds the crossing publishes (digit, above, count)
+//   S  sweep 2  float compare x >= value(digit) on the tiles; hits -> local stage buffer
+//      gather   stage buffer copied into EVERY peer's survivor list (DSMEM stores)
+//   S  finish   counting sort on an adaptive linear digit + exact rank inside buckets,
+//               ranking shared out over the cluster; first k written to global memory
+// When more than kSortCap elements sit at or above the threshold digit, further
+// digit levels run on the threshold bin's candidates before the finish.
 #pragma once
 
 #include <cooperative_groups.h>
@@ -24,9 +38,72 @@ namespace cg = cooperative_groups;
 // Dynamic shared memory layout (bytes).
 constexpr int kSmemHist = 0;                                   // uint32[kMaxBins]
 constexpr int kSmemStage = kSmemHist + kMaxBins * 4;           // uint64[kSortCap]; merged slice aliases its head
-constexpr int kSmemSort = kSmemStage + kSortCap * 8;           // uint64[kSortCap] (used on cluster rank 0)
+constexpr int kSmemSort = kSmemStage + kSortCap * 8;           // uint64[kSortCap] survivor list (every CTA)
 constexpr int kSmemCand = kSmemSort + kSortCap * 8;            // uint64[kCandCap]
-constexpr int kSmemBytes = kSmemCand + kCandCap * 8;
+constexpr int kSmemRing = kSmemCand + kCandCap * 8;            // ring of score tiles; work lists in the finish
+constexpr int kTileUnits = 1024;                               // 16-byte units per tile
+constexpr int kTileBytes = kTileUnits * 16;
+constexpr int kMinStages = 5;                                  // the finish needs 80 KiB of the ring area
+constexpr int kMaxStages = 7;
+constexpr int kWaitLimit = 1 << 22;                            // bounded mbarrier polling
+
+__host__ __device__ constexpr int smem_bytes_for(int stages) { return kSmemRing + stages * kTileBytes; }
+
+// ---- distributed shared memory primitives (PTX) ------------------------------
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ uint32_t dsmem_ld_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void dsmem_st_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void dsmem_st_u64(uint32_t addr, uint64_t v) {
+  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_atomic_add_u32(uint32_t addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
+}
+
+// ---- bulk asynchronous copies global -> shared, completion on an mbarrier -----
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Polls until the phase with the given parity has completed; gives up after
+// kWaitLimit polls and reports false so the caller can flag the launch.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (int i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
 
 // Geometry of one row as seen by one CTA of the cluster.  The row is cut into
 // 16-byte units on absolute addresses so interior units load as float4 even
@@ -80,57 +157,134 @@ __device__ __forceinline__ Chunk make_chunk(const float* row, const int32_t* ima
   return c;
 }
 
-// Calls f(key, index) once for every valid position of this CTA's chunk.
-template <bool HAS_MAP, typename F>
-__device__ __forceinline__ void for_each_in_chunk(const Chunk& c, F&& f) {
+// The (at most one) element of a partial first / last unit this thread owns:
+// returns its window position or -1, value in x.  Scalar load of a valid lane only.
+__device__ __forceinline__ int partial_element(const Chunk& c, float& x) {
+  int pos = -1;
+  if (threadIdx.x < 4 && c.head) {
+    pos = static_cast<int>(threadIdx.x) - c.mis;
+    if (pos >= 0 && pos < c.len) x = c.abase[threadIdx.x]; else pos = -1;
+  }
+  if (threadIdx.x >= 32 && threadIdx.x < 36 && c.tail) {
+    const int l4 = static_cast<int>(threadIdx.x) - 32;
+    pos = 4 * c.tail_unit - c.mis + l4;
+    if (pos >= 0 && pos < c.len) x = c.abase[4 * c.tail_unit + l4]; else pos = -1;
+  }
+  return pos;
+}
+
+// Generic (cold) sweep with direct global loads: calls f(x, index) for every
+// valid position of the chunk whose raw value passes pre(x).  Used in merge mode
+// and on the rare paths (deeper digit levels over a chunk that did not fit the
+// candidate buffer).  In merge mode f receives index -1 for ignored entries and
+// pre is not applied.
+template <bool HAS_MAP, typename Pre, typename F>
+__device__ __forceinline__ void for_each_in_chunk(const Chunk& c, Pre&& pre, F&& f) {
   if (HAS_MAP) {
-    // Merge mode: a few thousand (value, index) pairs in rank-strided segments.
     const float* vals = c.abase + c.mis;
     for (int i = c.pb + threadIdx.x; i < c.pe; i += kThreads) {
       const int64_t a = seg_addr(i, c.seg_len, c.seg_stride);
-      const int32_t idx = c.imap[a];
-      if (idx < 0) {
-        f(0u, -1);
-      } else {
-        f(key_of(vals[a]), idx);
-      }
+      f(vals[a], c.imap[a]);
     }
     return;
   }
   const float4* p4 = reinterpret_cast<const float4*>(c.abase);
-  auto one = [&](float x, int pos) { f(key_of(x), pos); };
-  auto unit = [&](const float4& v, int u) {
-    const int pos = 4 * u - c.mis;
-    one(v.x, pos);
-    one(v.y, pos + 1);
-    one(v.z, pos + 2);
-    one(v.w, pos + 3);
-  };
-  int u = c.fb + threadIdx.x;
-  for (; u + 3 * kThreads < c.fe; u += 4 * kThreads) {
-    const float4 v0 = __ldg(p4 + u);
-    const float4 v1 = __ldg(p4 + u + kThreads);
-    const float4 v2 = __ldg(p4 + u + 2 * kThreads);
-    const float4 v3 = __ldg(p4 + u + 3 * kThreads);
-    unit(v0, u);
-    unit(v1, u + kThreads);
-    unit(v2, u + 2 * kThreads);
-    unit(v3, u + 3 * kThreads);
-  }
-  for (; u < c.fe; u += kThreads) {
+#pragma unroll 1
+  for (int u = c.fb + threadIdx.x; u < c.fe; u += kThreads) {
     const float4 v = __ldg(p4 + u);
-    unit(v, u);
+    const int pos = 4 * u - c.mis;
+    if (pre(v.x)) f(v.x, pos);
+    if (pre(v.y)) f(v.y, pos + 1);
+    if (pre(v.z)) f(v.z, pos + 2);
+    if (pre(v.w)) f(v.w, pos + 3);
   }
-  // Partial first / last unit: scalar loads of the valid lanes only.
-  if (threadIdx.x < 4 && c.head) {
-    const int pos = static_cast<int>(threadIdx.x) - c.mis;
-    if (pos >= 0 && pos < c.len) one(c.abase[threadIdx.x], pos);
+  float x = 0.f;
+  const int pos = partial_element(c, x);
+  if (pos >= 0 && pre(x)) f(x, pos);
+}
+
+// ---- the hot sweeps: tiles of the chunk stream through a shared-memory ring ----
+struct TileStream {
+  const float4* src;   // global address of unit fb (16-byte aligned)
+  uint32_t ring;       // shared address of the ring
+  uint32_t bars;       // shared address of the per-stage mbarriers (8 bytes each)
+  int n_units;         // fe - fb
+  int n_tiles;
+  int stages;
+  bool timed_out;
+};
+
+__device__ __forceinline__ int tile_units(const TileStream& s, int t) {
+  return min(kTileUnits, s.n_units - t * kTileUnits);
+}
+__device__ __forceinline__ void issue_tile(const TileStream& s, int t) {
+  const int stage = t % s.stages;
+  const uint32_t bytes = static_cast<uint32_t>(tile_units(s, t)) * 16u;
+  const uint32_t bar = s.bars + 8u * stage;
+  mbar_expect_tx(bar, bytes);
+  bulk_load(s.ring + static_cast<uint32_t>(stage) * kTileBytes, s.src + static_cast<size_t>(t) * kTileUnits,
+            bytes, bar);
+}
+
+// First sweep: tiles 0..n-1 in order.  process(tile, t, units) is called by the
+// whole CTA once per tile with the tile's shared-memory address.
+template <typename F>
+__device__ __forceinline__ void stream_forward(TileStream& s, F&& process) {
+  if (threadIdx.x == 0) {
+    const int first = min(s.n_tiles, s.stages);
+    for (int t = 0; t < first; ++t) issue_tile(s, t);
   }
-  if (threadIdx.x >= 32 && threadIdx.x < 36 && c.tail) {
-    const int lane = static_cast<int>(threadIdx.x) - 32;
-    const int pos = 4 * c.tail_unit - c.mis + lane;
-    if (pos >= 0 && pos < c.len) one(c.abase[4 * c.tail_unit + lane], pos);
+#pragma unroll 1
+  for (int t = 0; t < s.n_tiles; ++t) {
+    const int stage = t % s.stages;
+    if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / s.stages) & 1))) s.timed_out = true;
+    process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
+    if (t + s.stages < s.n_tiles) {
+      __syncthreads();   // every thread is done with this stage before it is refilled
+      if (threadIdx.x == 0) issue_tile(s, t + s.stages);
+    }
   }
+}
+
+// Second sweep.  A chunk of at most `stages` tiles is still resident and is read
+// again with no copies at all.  Otherwise the ring holds the LAST `stages` tiles,
+// so the tiles are visited in reverse, refilling each stage with the tile
+// `stages` below it as soon as it has been consumed.
+template <typename F>
+__device__ __forceinline__ void stream_again(TileStream& s, F&& process) {
+#pragma unroll 1
+  for (int t = s.n_tiles - 1; t >= 0; --t) {
+    const int stage = t % s.stages;
+    if (t < s.n_tiles - s.stages) {
+      // refilled during this sweep: same parity as the tile's first visit
+      if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / s.stages) & 1))) s.timed_out = true;
+    }
+    process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
+    if (t - s.stages >= 0) {
+      __syncthreads();
+      if (threadIdx.x == 0) issue_tile(s, t - s.stages);
+    }
+  }
+}
+
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// Raw 12-bit digit of a score: sign | exponent | top 3 mantissa bits of x + 0.0f.
+// The add maps -0.0 to +0.0 and every NaN to the canonical 0x7fffffff, so the
+// digit needs no further special cases; raw_of_bin() translates between this
+// sign-magnitude order and the monotone bin order when the histogram is read.
+__device__ __forceinline__ uint32_t raw_digit(float x) { return __float_as_uint(__fadd_rn(x, 0.0f)) >> 20; }
+__device__ __forceinline__ int raw_of_bin(int m) { return m ^ ((m & 0x800) ? 0x800 : 0xfff); }
+
+// Key and composite of one element; ignored merge entries (index < 0) map to 0.
+template <bool HAS_MAP>
+__device__ __forceinline__ uint64_t comp_of(float x, int32_t idx) {
+  if (HAS_MAP && idx < 0) return 0ull;
+  return make_comp(key_of(x), idx);
 }
 
 struct ClusterShared {
@@ -141,76 +295,188 @@ struct ClusterShared {
   int sort_count;
   int cand_count;
   int push_base;
-  int table_row;
+  int small_count;
+  int big_count;
+  unsigned long long bars[kMaxStages + 1];
 };
+
+// Appends v to list[] with one shared atomic per group of converged lanes.
+__device__ __forceinline__ void push_aggregated(uint64_t* list, int* counter, int cap, uint64_t v) {
+  const unsigned mask = __activemask();
+  const int lane = threadIdx.x & 31;
+  const int leader = __ffs(mask) - 1;
+  int base = 0;
+  if (lane == leader) base = atomicAdd(counter, __popc(mask));
+  base = __shfl_sync(mask, base, leader);
+  const int pos = base + __popc(mask & ((1u << lane) - 1u));
+  if (pos < cap) list[pos] = v;
+}
+
+// Everything the per-element classification of one digit level needs.  The
+// classification is deliberately NOT inlined: it is the rare path of a sweep and
+// one copy keeps the kernel's instruction footprint small.
+struct LevelCtx {
+  uint64_t Pn;        // candidates have (comp >> shift) == Pn
+  uint64_t Pmax;      // this level's winners have Pn < (comp >> shift) <= Pmax
+  int shift;
+  int nshift;         // next level's digit: (comp >> nshift) & nmask
+  uint32_t nmask;
+  bool final_level;   // candidates are survivors too
+  bool compact;       // copy candidates into the CTA's candidate buffer
+  uint32_t* hist;
+  uint64_t* stage;
+  uint64_t* cand;
+  ClusterShared* sh;
+};
+
+__device__ __noinline__ void classify_comp(const LevelCtx* c, uint64_t comp) {
+  const uint64_t hi = comp >> c->shift;
+  if (hi == c->Pn) {
+    if (c->final_level) {
+      push_aggregated(c->stage, &c->sh->stage_count, kSortCap, comp);
+    } else {
+      atomicAdd(&c->hist[static_cast<uint32_t>(comp >> c->nshift) & c->nmask], 1u);
+      if (c->compact) push_aggregated(c->cand, &c->sh->cand_count, kCandCap, comp);
+    }
+  } else if (hi > c->Pn && hi <= c->Pmax) {
+    push_aggregated(c->stage, &c->sh->stage_count, kSortCap, comp);
+  }
+}
+
+template <bool HAS_MAP>
+__device__ __noinline__ void classify_value(const LevelCtx* c, float x, int32_t idx) {
+  classify_comp(c, comp_of<HAS_MAP>(x, idx));
+}
+
+// Second sweep over one tile: every value not below vmin is a hit; the hits'
+// composites are appended to list[0, cap).  A warp tests its 8 values per lane
+// with float compares and votes once; only a warp that saw a hit runs the
+// prefix scan and the single shared atomic that assign the list slots.
+__device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
+                                             uint64_t* list, int cap, int* counter) {
+  const int lane = threadIdx.x & 31;
+  float4 v[2];
+  uint32_t hits = 0u;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
+    if (lu < units) {
+      v[j] = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
+      const uint32_t h = (!(v[j].x < vmin) ? 1u : 0u) | (!(v[j].y < vmin) ? 2u : 0u) |
+                         (!(v[j].z < vmin) ? 4u : 0u) | (!(v[j].w < vmin) ? 8u : 0u);
+      hits |= h << (4 * j);
+    }
+  }
+  if (__any_sync(0xffffffffu, hits != 0u)) {
+    const int n = __popc(hits);
+    int incl = n;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += t;
+    }
+    int base = 0;
+    if (lane == 31) base = atomicAdd(counter, incl);
+    base = __shfl_sync(0xffffffffu, base, 31);
+    int pos = base + incl - n;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int first = 4 * (first_unit + static_cast<int>(threadIdx.x) + j * kThreads) - mis;
+      if ((hits >> (4 * j)) & 1u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].x), first); ++pos; }
+      if ((hits >> (4 * j)) & 2u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].y), first + 1); ++pos; }
+      if ((hits >> (4 * j)) & 4u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].z), first + 2); ++pos; }
+      if ((hits >> (4 * j)) & 8u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].w), first + 3); ++pos; }
+    }
+  }
+}
 
 // Cluster-wide histogram merge (reduce-scatter over distributed shared memory)
 // and suffix scan over the per-CTA slices.  On return every CTA's sh.res holds
 // the digit t with  #(digit > t) < r <= #(digit >= t), and those two counts.
+// raw0: the histogram is indexed by raw_digit() (first level of the fast path).
+// `merged` must not alias `hist`; with a single CTA the histogram is scanned in place.
 __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C, int rank,
                                                uint32_t* hist, uint32_t* merged, int nbins, int r,
-                                               ClusterShared& sh) {
+                                               bool raw0, ClusterShared& sh, const TopkParams& p, bool tr) {
   const int tid = threadIdx.x;
-  cluster.sync();  // every CTA's local histogram is complete and visible
   const int slice_n = nbins / C;
   const int slice_base = rank * slice_n;
-  for (int i = tid; i < slice_n; i += kThreads) {
-    uint32_t s = 0;
-    for (int c = 0; c < C; ++c) s += cluster.map_shared_rank(hist, c)[slice_base + i];
-    merged[i] = s;
+  if (C > 1) {
+    for (int i = tid; i < slice_n; i += kThreads) merged[i] = 0u;
   }
   if (tid == 0) sh.res[0] = -1;
-  __syncthreads();
+  if (C > 1) cluster.sync(); else __syncthreads();   // every CTA's local histogram is complete
+  if (tr) FF_TRACE(p, 26);
+  if (C > 1) {
+    // nbins loads per CTA in total, all independent: flat index -> (peer, bin of my slice)
+    const uint32_t hist_local = smem_addr(hist);
+    const int n_iter = nbins / kThreads;   // 8 for 4096 bins, 2 for 1024, 4 for 2048
+    uint32_t v[kMaxBins / kThreads];
+#pragma unroll
+    for (int j = 0; j < kMaxBins / kThreads; ++j) {
+      if (j < n_iter) {
+        const int flat = tid + j * kThreads;
+        const int peer = flat / slice_n;
+        int b = slice_base + (flat - peer * slice_n);
+        if (raw0) b = raw_of_bin(b);
+        v[j] = dsmem_ld_u32(dsmem_addr(hist_local + 4u * static_cast<uint32_t>(b), peer));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxBins / kThreads; ++j) {
+      if (j < n_iter) {
+        const int flat = tid + j * kThreads;
+        if (v[j] != 0u) atomicAdd(&merged[flat % slice_n], v[j]);
+      }
+    }
+    __syncthreads();
+  }
+  if (tr) FF_TRACE(p, 27);
+  // slice value i: merged[i], or (single CTA) the histogram itself in monotone order
+  auto slice_at = [&](int i) -> int {
+    if (C > 1) return static_cast<int>(merged[i]);
+    return static_cast<int>(hist[raw0 ? raw_of_bin(i) : i]);
+  };
   const int per = slice_n >= kThreads ? slice_n / kThreads : 1;
   const int first = tid * per;
   int local = 0;
   if (first < slice_n) {
-    for (int e = 0; e < per; ++e) local += static_cast<int>(merged[first + e]);
+    for (int e = 0; e < per; ++e) local += slice_at(first + e);
   }
   int total;
   const int excl = block_suffix_exclusive(local, sh.warp_tot, total);
-  if (tid < C) cluster.map_shared_rank(sh.slice_tot, tid)[rank] = total;
-  cluster.sync();  // slice totals of every CTA have arrived
+  if (tr) FF_TRACE(p, 28);
+  if (C > 1) {
+    if (tid < C) dsmem_st_u32(dsmem_addr(smem_addr(&sh.slice_tot[rank]), tid), static_cast<uint32_t>(total));
+    cluster.sync();  // slice totals of every CTA have arrived
+  }
+  if (tr) FF_TRACE(p, 29);
   int above_slice = 0;
   for (int c = rank + 1; c < C; ++c) above_slice += sh.slice_tot[c];
   if (first < slice_n) {
     int running = above_slice + excl;
     for (int e = per - 1; e >= 0; --e) {
-      const int cnt = static_cast<int>(merged[first + e]);
+      const int cnt = slice_at(first + e);
       const int next = running;
       running += cnt;
       if (next < r && r <= running) {
-        for (int c = 0; c < C; ++c) {
-          int* rr = cluster.map_shared_rank(sh.res, c);
-          rr[1] = next;
-          rr[2] = cnt;
-          rr[0] = slice_base + first + e;
+        if (C > 1) {
+          for (int c = 0; c < C; ++c) {
+            const uint32_t a = dsmem_addr(smem_addr(&sh.res[0]), c);
+            dsmem_st_u32(a + 4, static_cast<uint32_t>(next));
+            dsmem_st_u32(a + 8, static_cast<uint32_t>(cnt));
+            dsmem_st_u32(a, static_cast<uint32_t>(slice_base + first + e));
+          }
+        } else {
+          sh.res[1] = next;
+          sh.res[2] = cnt;
+          sh.res[0] = slice_base + first + e;
         }
       }
     }
   }
-  cluster.sync();  // the threshold triple has arrived everywhere
-}
-
-// Descending bitonic sort of buf[0, n) (n a power of two) in shared memory.
-__device__ __forceinline__ void bitonic_sort_desc(uint64_t* buf, int n) {
-  for (int size = 2; size <= n; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      __syncthreads();
-      for (int q = threadIdx.x; q < (n >> 1); q += kThreads) {
-        const int i = 2 * q - (q & (stride - 1));
-        const int j = i + stride;
-        const uint64_t a = buf[i];
-        const uint64_t b = buf[j];
-        const bool desc = (i & size) == 0;
-        if ((a < b) == desc) {
-          buf[i] = b;
-          buf[j] = a;
-        }
-      }
-    }
-  }
-  __syncthreads();
+  if (tr) FF_TRACE(p, 30);
+  if (C > 1) cluster.sync(); else __syncthreads();   // the threshold triple has arrived everywhere
 }
 
 // Writes output slot j of `row` from a window-relative index (or -1) and key.
@@ -233,9 +499,16 @@ __device__ __forceinline__ void emit(const TopkParams& p, int row, int j, int32_
   }
 }
 
+// Smallest float whose key is >= key_lo (clamped to +inf where key_lo lies in
+// the NaN range): x passes the pre-filter iff !(x < value), which keeps NaN.
+__device__ __forceinline__ float prefilter_value(uint32_t key_lo) {
+  if (key_lo > 0xff800000u) key_lo = 0xff800000u;
+  return __uint_as_float(bits_of_key(key_lo));
+}
+
 template <bool HAS_MAP>
-__global__ void __launch_bounds__(kThreads) topk_cluster_kernel(const TopkParams p) {
-  extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
   __shared__ ClusterShared sh;
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
@@ -300,16 +573,53 @@ __global__ void __launch_bounds__(kThreads) topk_cluster_kernel(const TopkParams
   }
 
   const Chunk chunk = make_chunk(rowp, imap, len, C, rank, p.seg_len, p.seg_stride);
+  FF_TRACE(p, 0);
 
   // ---- level 0: 12-bit histogram of the whole chunk -----------------------
   for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
+  TileStream ts;
+  ts.src = reinterpret_cast<const float4*>(chunk.abase) + chunk.fb;
+  ts.ring = smem_addr(smem + kSmemRing);
+  ts.bars = smem_addr(&sh.bars[0]);
+  ts.n_units = chunk.fe - chunk.fb;
+  ts.n_tiles = (ts.n_units + kTileUnits - 1) / kTileUnits;
+  ts.stages = p.ring_stages;
+  ts.timed_out = false;
   if (tid == 0) {
     sh.stage_count = 0;
     sh.sort_count = 0;
     sh.cand_count = 0;
+    sh.small_count = 0;
+    sh.big_count = 0;
+    if (!HAS_MAP) {
+      for (int s = 0; s < ts.stages; ++s) mbar_init(ts.bars + 8u * s, 1u);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
   }
   __syncthreads();
-  for_each_in_chunk<HAS_MAP>(chunk, [&](uint32_t key, int32_t) { atomicAdd(&hist[key >> 20], 1u); });
+  if (HAS_MAP) {
+    for_each_in_chunk<true>(
+        chunk, [](float) { return true; },
+        [&](float x, int32_t idx) { atomicAdd(&hist[(idx < 0 ? 0u : key_of(x)) >> 20], 1u); });
+  } else {
+    stream_forward(ts, [&](uint32_t tile, int, int units) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int lu = tid + j * kThreads;
+        if (lu < units) {
+          const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
+          atomicAdd(&hist[raw_digit(v.x)], 1u);
+          atomicAdd(&hist[raw_digit(v.y)], 1u);
+          atomicAdd(&hist[raw_digit(v.z)], 1u);
+          atomicAdd(&hist[raw_digit(v.w)], 1u);
+        }
+      }
+    });
+    float x = 0.f;
+    if (partial_element(chunk, x) >= 0) atomicAdd(&hist[raw_digit(x)], 1u);
+  }
+  __syncthreads();
+  FF_TRACE(p, 1);
 
   int r = k;                // survivors still to be taken from the current candidate set
   uint64_t P = 0;           // digits fixed so far (value of comp >> shift of the last level)
@@ -317,11 +627,15 @@ __global__ void __launch_bounds__(kThreads) topk_cluster_kernel(const TopkParams
   int cand_n = 0;
   bool ok = true;
   int expected_total = 0;
+  uint64_t floor_comp = 0;  // no survivor's composite is below this
 
+#pragma unroll 1
   for (int level = 0; level < kNumLevels; ++level) {
     const int bits = level_bits(level);
     const int shift = level_shift(level);
-    merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, sh);
+    const bool raw0 = !HAS_MAP && level == 0;
+    merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0);
+    FF_TRACE(p, 2 + 3 * level);
     const int t = sh.res[0];
     const int above = sh.res[1];
     const int m = sh.res[2];
@@ -333,7 +647,7 @@ __global__ void __launch_bounds__(kThreads) topk_cluster_kernel(const TopkParams
     const bool final_level = total <= kSortCap || level == kNumLevels - 1;
     const uint64_t Pn = (level == 0 ? 0ull : (P << bits)) | static_cast<uint64_t>(t);
     const uint64_t Pmax = Pn | ((1ull << bits) - 1ull);
-    const int local_m = static_cast<int>(hist[t]);
+    const int local_m = static_cast<int>(hist[raw0 ? raw_of_bin(t) : t]);
     const bool compact = !final_level && !src_is_cand && local_m <= kCandCap;
     const int nshift = final_level ? 0 : level_shift(level + 1);
     const uint32_t nmask = final_level ? 0u : ((1u << level_bits(level + 1)) - 1u);
@@ -343,74 +657,265 @@ __global__ void __launch_bounds__(kThreads) topk_cluster_kernel(const TopkParams
     }
     __syncthreads();
 
-    auto classify = [&](uint64_t comp) {
-      const uint64_t hi = comp >> shift;
-      if (hi == Pn) {
-        if (final_level) {
-          const int pos = atomicAdd(&sh.stage_count, 1);
-          if (pos < kSortCap) stage[pos] = comp;
-        } else {
-          atomicAdd(&hist[static_cast<uint32_t>(comp >> nshift) & nmask], 1u);
-          if (compact) {
-            const int pos = atomicAdd(&sh.cand_count, 1);
-            if (pos < kCandCap) cand[pos] = comp;
-          }
-        }
-      } else if (hi > Pn && hi <= Pmax) {
-        const int pos = atomicAdd(&sh.stage_count, 1);
-        if (pos < kSortCap) stage[pos] = comp;
+    FF_TRACE(p, 16);
+    LevelCtx ctx;
+    ctx.Pn = Pn;
+    ctx.Pmax = Pmax;
+    ctx.shift = shift;
+    ctx.nshift = nshift;
+    ctx.nmask = nmask;
+    ctx.final_level = final_level;
+    ctx.compact = compact;
+    ctx.hist = hist;
+    ctx.stage = stage;
+    ctx.cand = cand;
+    ctx.sh = &sh;
+    // At level 0 "digit >= t" is exactly "value >= value(t << 20)" (unless t lies in
+    // the NaN range), so the chunk is swept with float compares only.
+    bool swept = false;
+    if (!HAS_MAP && level == 0 && (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
+      const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
+      uint64_t* list = final_level ? stage : cand;
+      int* counter = final_level ? &sh.stage_count : &sh.cand_count;
+      const int cap = final_level ? kSortCap : kCandCap;
+      stream_again(ts, [&](uint32_t tile, int tt, int units) {
+        collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, list, cap, counter);
+        if (tt < 8) FF_TRACE(p, 8 + tt);
+      });
+      float x = 0.f;
+      const int pos = partial_element(chunk, x);
+      if (pos >= 0 && !(x < vmin)) {
+        const int slot = atomicAdd(counter, 1);
+        if (slot < cap) list[slot] = make_comp(key_of(x), pos);
       }
-    };
-    if (src_is_cand) {
-      for (int i = tid; i < cand_n; i += kThreads) classify(cand[i]);
+      if (final_level) {
+        swept = true;
+      } else {
+        // winners and candidates together; they are classified from the buffer
+        __syncthreads();
+        if (sh.cand_count <= kCandCap) {
+          src_is_cand = true;
+          cand_n = sh.cand_count;
+          ctx.compact = false;
+        } else {
+          __syncthreads();
+          if (tid == 0) sh.cand_count = 0;   // too many for the buffer: generic sweep below
+          __syncthreads();
+        }
+      }
+    }
+    if (swept) {
+      // nothing left to do for this level
+    } else if (src_is_cand) {
+      for (int i = tid; i < cand_n; i += kThreads) classify_comp(&ctx, cand[i]);
     } else {
-      for_each_in_chunk<HAS_MAP>(chunk,
-                                 [&](uint32_t key, int32_t idx) { classify(make_comp(key, idx)); });
+      // Everything of interest has composite >= Pn << shift, i.e. value >= vmin.
+      const float vmin = prefilter_value(static_cast<uint32_t>((Pn << shift) >> 32));
+      for_each_in_chunk<HAS_MAP>(
+          chunk, [vmin](float x) { return !(x < vmin); },
+          [&](float x, int32_t idx) { classify_value<HAS_MAP>(&ctx, x, idx); });
     }
     __syncthreads();
+    FF_TRACE(p, 3 + 3 * level);
 
-    // Move this CTA's survivors into rank 0's sort buffer: one remote atomic
-    // reserves a contiguous block, then coalesced remote stores fill it.
+    // All-gather this CTA's survivors into EVERY peer's survivor list: one remote
+    // atomic on rank 0 reserves a block of slots (the same in every copy), then
+    // coalesced remote stores fill it.  Each CTA ends up with the full list and
+    // can take a share of the finishing work without further exchange.
     const int n_stage = min(sh.stage_count, kSortCap);
     if (n_stage > 0) {
-      if (tid == 0) sh.push_base = atomicAdd(&cluster.map_shared_rank(&sh, 0)->sort_count, n_stage);
-      __syncthreads();
-      uint64_t* dst = cluster.map_shared_rank(sortbuf, 0);
-      const int base = sh.push_base;
-      for (int i = tid; i < n_stage; i += kThreads) {
-        if (base + i < kSortCap) dst[base + i] = stage[i];
+      if (C == 1) {
+        const int base = sh.sort_count;
+        __syncthreads();
+        for (int i = tid; i < n_stage; i += kThreads) {
+          if (base + i < kSortCap) sortbuf[base + i] = stage[i];
+        }
+        if (tid == 0) sh.sort_count = base + n_stage;
+      } else {
+        if (tid == 0) {
+          sh.push_base = static_cast<int>(dsmem_atomic_add_u32(
+              dsmem_addr(smem_addr(&sh.sort_count), 0), static_cast<uint32_t>(n_stage)));
+        }
+        __syncthreads();
+        const int base = sh.push_base;
+        const uint32_t sort_local = smem_addr(sortbuf);
+        for (int j = tid; j < n_stage * C; j += kThreads) {
+          const int c = j / n_stage;
+          const int i = j - c * n_stage;
+          if (base + i < kSortCap)
+            dsmem_st_u64(dsmem_addr(sort_local + 8u * static_cast<uint32_t>(base + i), c), stage[i]);
+        }
       }
     }
     __syncthreads();
+    FF_TRACE(p, 4 + 3 * level);
     if (tid == 0) sh.stage_count = 0;
-    if (compact) {
+    if (ctx.compact && !src_is_cand) {
       src_is_cand = true;
       cand_n = min(sh.cand_count, kCandCap);
     }
     if (final_level) {
       expected_total = total;
+      floor_comp = Pn << shift;
       break;
     }
     r -= above;
     P = Pn;
   }
 
-  cluster.sync();  // every survivor has landed in rank 0's sort buffer
-  if (rank != 0) return;
+  if (C > 1) cluster.sync(); else __syncthreads();   // every survivor has landed in every CTA's list
+  FF_TRACE(p, 20);
 
-  // ---- finishing sort on the cluster's first CTA --------------------------
-  int T = ok ? min(sh.sort_count, kSortCap) : 0;
-  if (ok && T != expected_total && p.status != nullptr && tid == 0)
-    atomicOr(p.status, 1);
-  if (!ok && p.status != nullptr && tid == 0) atomicOr(p.status, 4);
-  int n = 32;
-  while (n < T) n <<= 1;
-  for (int i = T + tid; i < n; i += kThreads) sortbuf[i] = 0ull;
-  bitonic_sort_desc(sortbuf, n);
-  for (int j = tid; j < k; j += kThreads) {
-    const uint64_t c = j < T ? sortbuf[j] : 0ull;
-    emit(p, row, j, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+  if (ts.timed_out && p.status != nullptr && tid == 0) atomicOr(p.status, 2);
+  if (!ok) {
+    if (p.status != nullptr && tid == 0 && rank == 0) atomicOr(p.status, 4);
+    if (rank == 0) {
+      for (int j = tid; j < k; j += kThreads) emit(p, row, j, -1, 0u, HAS_MAP, table_row);
+    }
+    return;
   }
+  const int T = min(expected_total, kSortCap);
+  if (rank == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
+    atomicOr(p.status, 1);
+
+  // ---- finish: rank the T survivors and write the first k ------------------
+  // A counting sort on an adaptive linear digit: bin = (comp - floor) >> shift
+  // with shift chosen so the survivors' composite range spans <= 4096 bins (any
+  // monotone bin map keeps the result exact).  Every CTA builds the same
+  // buckets from its copy of the survivor list, each thread holding up to 8
+  // survivors in registers.  A survivor alone in its bucket is placed at once;
+  // the others are ranked inside their bucket by counting, and that work is
+  // shared out over the cluster by element: small buckets by one thread per
+  // element, large ones (heavy ties) by 8 lanes per element.
+  constexpr int kPer = kSortCap / kThreads;
+  uint32_t* bucket_start = reinterpret_cast<uint32_t*>(smem + kSmemCand);        // #(bin > b)
+  uint64_t* bucketed = stage;
+  ulonglong2* small_list = reinterpret_cast<ulonglong2*>(smem + kSmemRing);        // kSortCap x 16 B
+  int* big_list = reinterpret_cast<int*>(smem + kSmemRing + kSortCap * 16);        // kSortCap x 4 B
+  uint64_t e[kPer];
+  uint32_t hmax = 0u;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int i = tid + j * kThreads;
+    e[j] = i < T ? sortbuf[i] : 0ull;
+    hmax = max(hmax, static_cast<uint32_t>(e[j] >> 32));
+  }
+  hmax = __reduce_max_sync(0xffffffffu, hmax);
+  if ((tid & 31) == 0) sh.warp_tot[tid >> 5] = static_cast<int>(hmax);
+  for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) hmax = max(hmax, static_cast<uint32_t>(sh.warp_tot[w]));
+  const uint64_t lo = floor_comp;
+  const uint64_t span = ((static_cast<uint64_t>(hmax) << 32) | 0xffffffffull) - lo;
+  const int nbits = span == 0ull ? 0 : 64 - __clzll(static_cast<long long>(span));
+  const int bshift = nbits > 12 ? nbits - 12 : 0;
+  uint32_t bin[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    bin[j] = static_cast<uint32_t>((e[j] - lo) >> bshift);
+    if (tid + j * kThreads < T) atomicAdd(&hist[bin[j]], 1u);
+  }
+  __syncthreads();
+  FF_TRACE(p, 22);
+  {
+    constexpr int per = kMaxBins / kThreads;
+    int local = 0;
+#pragma unroll
+    for (int q = 0; q < per; ++q) local += static_cast<int>(hist[tid * per + q]);
+    int total;
+    int running = block_suffix_exclusive(local, sh.warp_tot, total);
+#pragma unroll
+    for (int q = per - 1; q >= 0; --q) {
+      const int b = tid * per + q;
+      bucket_start[b] = static_cast<uint32_t>(running);
+      running += static_cast<int>(hist[b]);
+      hist[b] = 0u;   // becomes the scatter cursor
+    }
+  }
+  __syncthreads();
+  FF_TRACE(p, 23);
+  uint32_t begin[kPer], at[kPer];   // bucket start and slot of e[j] in the bucketed array
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    if (tid + j * kThreads < T) {
+      begin[j] = bucket_start[bin[j]];
+      at[j] = begin[j] + atomicAdd(&hist[bin[j]], 1u);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    if (tid + j * kThreads < T) bucketed[at[j]] = e[j];
+  }
+  __syncthreads();
+  FF_TRACE(p, 24);
+  // Scatter order inside a bucket differs from CTA to CTA (atomics), so the
+  // ranking work is shared out by element identity, not by array position.
+  constexpr int kSmallBucket = 8;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    if (tid + j * kThreads >= T) continue;
+    const uint64_t c = e[j];
+    if (static_cast<int>(begin[j]) >= k) continue;
+    if ((static_cast<uint32_t>(c) & static_cast<uint32_t>(C - 1)) != static_cast<uint32_t>(rank)) continue;
+    const uint32_t n_b = hist[bin[j]];
+    if (n_b == 1u) {
+      emit(p, row, static_cast<int>(begin[j]), c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    } else if (n_b <= kSmallBucket) {
+      const int slot = atomicAdd(&sh.small_count, 1);
+      small_list[slot] = make_ulonglong2(c, static_cast<uint64_t>(at[j]) | (static_cast<uint64_t>(begin[j]) << 16) |
+                                                (static_cast<uint64_t>(n_b) << 32));
+    } else {
+      big_list[atomicAdd(&sh.big_count, 1)] = static_cast<int>(at[j]);
+    }
+  }
+  FF_TRACE(p, 31);
+  __syncthreads();
+  {
+    const int n_small = sh.small_count;
+    for (int i = tid; i < n_small; i += kThreads) {
+      const ulonglong2 it = small_list[i];
+      const uint64_t c = it.x;
+      const int me = static_cast<int>(it.y & 0xffffu);
+      const int b0 = static_cast<int>((it.y >> 16) & 0xffffu);
+      const int n_b = static_cast<int>(it.y >> 32);
+      int pos = b0;
+#pragma unroll
+      for (int q = 0; q < kSmallBucket; ++q) {
+        if (q < n_b) {
+          const uint64_t o = bucketed[b0 + q];
+          pos += (o > c || (o == c && b0 + q < me)) ? 1 : 0;
+        }
+      }
+      if (pos < k) emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    }
+  }
+  {
+    const int n_big = sh.big_count;
+    const int group = tid >> 3, sub = tid & 7;
+    // the trip count is uniform over the CTA so every lane reaches the shuffles
+    for (int d0 = 0; d0 < n_big; d0 += kThreads / 8) {
+      const int d = d0 + group;
+      const bool active = d < n_big;
+      const int me = active ? big_list[d] : 0;
+      const uint64_t c = bucketed[me];
+      const uint32_t b = static_cast<uint32_t>((c - lo) >> bshift);
+      const int b0 = static_cast<int>(bucket_start[b]);
+      const int end = active ? b0 + static_cast<int>(hist[b]) : b0;
+      int cnt = 0;
+      for (int q = b0 + sub; q < end; q += 8) {
+        const uint64_t o = bucketed[q];
+        cnt += (o > c || (o == c && q < me)) ? 1 : 0;
+      }
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
+      cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
+      const int pos = b0 + cnt;
+      if (active && sub == 0 && pos < k)
+        emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    }
+  }
+  FF_TRACE(p, 25);
 }
 
 }  // namespace ff

@@ -123,6 +123,13 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
  * (0 = automatic policy, else 1, 2, 4, 8 or 16).  Process-wide. */
 int ff_topk_set_cluster_override(int32_t cluster_size);
 
+/* Debug aid: when non-NULL, every CTA of every later launch writes its stage
+ * time stamps (SM cycle counter) to device_buffer[cta * 32 + slot] (uint64).
+ * The buffer must hold 32 words per CTA of the largest launch.  Process-wide;
+ * pass NULL to switch tracing off.  Plays the role of the reference's
+ * SMALL_K_PROFILE clock64 brackets (top_small_k.cuh:39-41,132-135). */
+int ff_topk_set_trace_buffer(void* device_buffer);
+
 /* The cluster size the automatic policy picks for (B, L_width, k) on the
  * current device (after overrides). */
 int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k);

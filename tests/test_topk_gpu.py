@@ -137,6 +137,8 @@ def test_special_values(ff, oracle):
     s[0, 2::1000] = float("nan")
     s[0, 3::1000] = float("inf")
     s[0, 4::1000] = float("-inf")
+    s[0].view(torch.int32)[7::1000] = -4194304 + 5       # negative NaN with a payload (0xFFC00005)
+    s[0].view(torch.int32)[8::1000] = 0x7F800001          # signalling NaN
     s[1] = s[1].abs() * 1e-42                            # denormals
     lengths = torch.tensor([50000, 50000], dtype=torch.int32)
     for k in (16, 512, 2048):
