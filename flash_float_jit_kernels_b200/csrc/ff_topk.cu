@@ -98,9 +98,9 @@ int pow2_ceil(int64_t v) {
 }
 
 // Cluster size per row.  One CTA sweeps about 16 Ki scores; the cluster grows
-// with the row up to the largest size the device can schedule.
+// with the row up to the largest size the device can schedule, but not beyond
+// what lets every row of the batch run at the same time.
 int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
-  (void)B;
   (void)k;
   int c = g_cluster_override.load();
   if (c == 0) {
@@ -110,6 +110,10 @@ int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
   if (c == 0) {
     c = pow2_ceil((L_width + 16383) / 16384);
     if (c < 1) c = 1;
+    // Keep the whole batch in one wave of CTAs (one CTA per SM) when it fits.
+    int fit = 1;
+    while (fit * 2 * static_cast<int64_t>(B) <= g_sm_count[device] && fit < ff::kMaxCluster) fit *= 2;
+    if (c > fit) c = fit;
   }
   if (c > ff::kMaxCluster) c = ff::kMaxCluster;
   if (c > g_max_cluster[device]) c = g_max_cluster[device];
@@ -132,7 +136,7 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   cfg.numAttrs = 1;
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
-  q.ring_stages = ff::kMaxStages;
+
   cudaError_t e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP>, q);
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx(topk_cluster_kernel)");
   g_launches.fetch_add(1, std::memory_order_relaxed);

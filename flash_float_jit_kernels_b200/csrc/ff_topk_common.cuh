@@ -68,7 +68,6 @@ struct TopkParams {
   int64_t shard_offset;        // context-parallel: first global column of this shard
   int32_t fixed_len;           // >= 0: every row has this many positions (merge mode)
   int32_t epilogue;            // FF_EPILOGUE_*
-  int32_t ring_stages;         // shared-memory tiles in the streaming ring (kMinStages..kMaxStages)
   const int32_t* table;        // page table
   int64_t table_stride;
   const int32_t* cu_seqlens_q; // prefill row -> request map, or null

@@ -41,10 +41,12 @@ constexpr int kSmemStage = kSmemHist + kMaxBins * 4;           // uint64[kSortCa
 constexpr int kSmemSort = kSmemStage + kSortCap * 8;           // uint64[kSortCap] survivor list (every CTA)
 constexpr int kSmemCand = kSmemSort + kSortCap * 8;            // uint64[kCandCap]
 constexpr int kSmemRing = kSmemCand + kCandCap * 8;            // ring of score tiles; work lists in the finish
-constexpr int kTileUnits = 1024;                               // 16-byte units per tile
+constexpr int kTileUnits = 2048;                               // 16-byte units per tile (32 KiB)
 constexpr int kTileBytes = kTileUnits * 16;
-constexpr int kMinStages = 5;                                  // the finish needs 80 KiB of the ring area
-constexpr int kMaxStages = 7;
+static_assert(kTileUnits % kThreads == 0 && kTileUnits / kThreads <= 4, "a thread reads at most 4 units of a tile");
+constexpr int kStages = 3;                                     // tiles in the ring (96 KiB)
+constexpr int kMinStages = kStages;
+constexpr int kMaxStages = kStages;
 constexpr int kWaitLimit = 1 << 22;                            // bounded mbarrier polling
 
 __host__ __device__ constexpr int smem_bytes_for(int stages) { return kSmemRing + stages * kTileBytes; }
@@ -207,10 +209,10 @@ __device__ __forceinline__ void for_each_in_chunk(const Chunk& c, Pre&& pre, F&&
 struct TileStream {
   const float4* src;   // global address of unit fb (16-byte aligned)
   uint32_t ring;       // shared address of the ring
-  uint32_t bars;       // shared address of the per-stage mbarriers (8 bytes each)
+  uint32_t bars;       // shared address of the per-stage "full" mbarriers (8 bytes each)
+  uint32_t ebars;      // shared address of the per-stage "empty" mbarriers
   int n_units;         // fe - fb
   int n_tiles;
-  int stages;
   bool timed_out;
 };
 
@@ -218,7 +220,7 @@ __device__ __forceinline__ int tile_units(const TileStream& s, int t) {
   return min(kTileUnits, s.n_units - t * kTileUnits);
 }
 __device__ __forceinline__ void issue_tile(const TileStream& s, int t) {
-  const int stage = t % s.stages;
+  const int stage = t % kStages;
   const uint32_t bytes = static_cast<uint32_t>(tile_units(s, t)) * 16u;
   const uint32_t bar = s.bars + 8u * stage;
   mbar_expect_tx(bar, bytes);
@@ -226,43 +228,71 @@ __device__ __forceinline__ void issue_tile(const TileStream& s, int t) {
             bytes, bar);
 }
 
-// First sweep: tiles 0..n-1 in order.  process(tile, t, units) is called by the
-// whole CTA once per tile with the tile's shared-memory address.
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// The ring is refilled without any CTA-wide barrier: every warp arrives on the
+// stage's "empty" mbarrier when it has read its part of the tile, and thread 0
+// refills the stage that was consumed kRefillLag tiles ago, so it rarely has to
+// wait for a slower warp while stages - kRefillLag tiles stay in flight.
+constexpr int kRefillLag = 1;
+
+// First sweep: tiles 0..n-1 in order.  process(tile, t, units) is called by
+// every thread once per tile with the tile's shared-memory address.
 template <typename F>
 __device__ __forceinline__ void stream_forward(TileStream& s, F&& process) {
+  const bool refill = s.n_tiles > kStages;
   if (threadIdx.x == 0) {
-    const int first = min(s.n_tiles, s.stages);
+    const int first = min(s.n_tiles, kStages);
     for (int t = 0; t < first; ++t) issue_tile(s, t);
   }
 #pragma unroll 1
   for (int t = 0; t < s.n_tiles; ++t) {
-    const int stage = t % s.stages;
-    if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / s.stages) & 1))) s.timed_out = true;
+    const int stage = t % kStages;
+    if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / kStages) & 1))) s.timed_out = true;
     process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
-    if (t + s.stages < s.n_tiles) {
-      __syncthreads();   // every thread is done with this stage before it is refilled
-      if (threadIdx.x == 0) issue_tile(s, t + s.stages);
+    if (refill) {
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(s.ebars + 8u * stage);
+      const int tr = t - kRefillLag + kStages;
+      if (threadIdx.x == 0 && t >= kRefillLag && tr < s.n_tiles) {
+        // fill number q of a stage waits for the (q-1)-th "all warps done" of that stage
+        const int q = tr / kStages;
+        if (!mbar_wait(s.ebars + 8u * (tr % kStages), static_cast<uint32_t>((q - 1) & 1))) s.timed_out = true;
+        issue_tile(s, tr);
+      }
     }
   }
 }
 
 // Second sweep.  A chunk of at most `stages` tiles is still resident and is read
 // again with no copies at all.  Otherwise the ring holds the LAST `stages` tiles,
-// so the tiles are visited in reverse, refilling each stage with the tile
-// `stages` below it as soon as it has been consumed.
+// so the tiles are visited in reverse, each stage being refilled with the tile
+// `stages` below the one just consumed.  Phase bookkeeping: during the first
+// sweep stage s completed its "empty" barrier once per tile it held; here the
+// refill that brings in the tile with q = t / stages waits for the completion of
+// index 2 * fills(s) - 2 - q, whose parity is q & 1, and the tile's "full"
+// barrier completes with parity q & 1 as on its first visit.
 template <typename F>
 __device__ __forceinline__ void stream_again(TileStream& s, F&& process) {
+  const bool refill = s.n_tiles > kStages;
 #pragma unroll 1
   for (int t = s.n_tiles - 1; t >= 0; --t) {
-    const int stage = t % s.stages;
-    if (t < s.n_tiles - s.stages) {
-      // refilled during this sweep: same parity as the tile's first visit
-      if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / s.stages) & 1))) s.timed_out = true;
+    const int stage = t % kStages;
+    if (t < s.n_tiles - kStages) {
+      if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / kStages) & 1))) s.timed_out = true;
     }
     process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
-    if (t - s.stages >= 0) {
-      __syncthreads();
-      if (threadIdx.x == 0) issue_tile(s, t - s.stages);
+    if (refill) {
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(s.ebars + 8u * stage);
+      const int tr = t + kRefillLag - kStages;
+      if (threadIdx.x == 0 && t + kRefillLag <= s.n_tiles - 1 && tr >= 0) {
+        if (!mbar_wait(s.ebars + 8u * (tr % kStages), static_cast<uint32_t>((tr / kStages) & 1)))
+          s.timed_out = true;
+        issue_tile(s, tr);
+      }
     }
   }
 }
@@ -298,6 +328,7 @@ struct ClusterShared {
   int small_count;
   int big_count;
   unsigned long long bars[kMaxStages + 1];
+  unsigned long long ebars[kMaxStages + 1];
 };
 
 // Appends v to list[] with one shared atomic per group of converged lanes.
@@ -349,43 +380,48 @@ __device__ __noinline__ void classify_value(const LevelCtx* c, float x, int32_t 
 }
 
 // Second sweep over one tile: every value not below vmin is a hit; the hits'
-// composites are appended to list[0, cap).  A warp tests its 8 values per lane
-// with float compares and votes once; only a warp that saw a hit runs the
-// prefix scan and the single shared atomic that assign the list slots.
+// composites are appended to list[0, cap).  A warp tests its 16 values per lane
+// with float compares and votes once.  Only a warp that saw a hit assigns list
+// slots: the per-lane hit counts (0..16) are prefix-summed with five ballots over
+// their bit planes, one lane does the single shared atomic, and each lane then
+// walks its own hit bits, re-reading the value from the tile.
 __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
                                              uint64_t* list, int cap, int* counter) {
   const int lane = threadIdx.x & 31;
-  float4 v[2];
   uint32_t hits = 0u;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
+  for (int j = 0; j < kTileUnits / kThreads; ++j) {
     const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
     if (lu < units) {
-      v[j] = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
-      const uint32_t h = (!(v[j].x < vmin) ? 1u : 0u) | (!(v[j].y < vmin) ? 2u : 0u) |
-                         (!(v[j].z < vmin) ? 4u : 0u) | (!(v[j].w < vmin) ? 8u : 0u);
+      const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
+      const uint32_t h = (!(v.x < vmin) ? 1u : 0u) | (!(v.y < vmin) ? 2u : 0u) |
+                         (!(v.z < vmin) ? 4u : 0u) | (!(v.w < vmin) ? 8u : 0u);
       hits |= h << (4 * j);
     }
   }
   if (__any_sync(0xffffffffu, hits != 0u)) {
-    const int n = __popc(hits);
-    int incl = n;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, off);
-      if (lane >= off) incl += t;
-    }
+    const uint32_t n = __popc(hits);
+    const uint32_t lt = (1u << lane) - 1u;
+    const uint32_t b0 = __ballot_sync(0xffffffffu, n & 1u);
+    const uint32_t b1 = __ballot_sync(0xffffffffu, n & 2u);
+    const uint32_t b2 = __ballot_sync(0xffffffffu, n & 4u);
+    const uint32_t b3 = __ballot_sync(0xffffffffu, n & 8u);
+    const uint32_t b4 = __ballot_sync(0xffffffffu, n & 16u);
+    const int before = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt) + 8 * __popc(b3 & lt) +
+                       16 * __popc(b4 & lt);
+    const int total = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3) + 16 * __popc(b4);
     int base = 0;
-    if (lane == 31) base = atomicAdd(counter, incl);
-    base = __shfl_sync(0xffffffffu, base, 31);
-    int pos = base + incl - n;
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const int first = 4 * (first_unit + static_cast<int>(threadIdx.x) + j * kThreads) - mis;
-      if ((hits >> (4 * j)) & 1u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].x), first); ++pos; }
-      if ((hits >> (4 * j)) & 2u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].y), first + 1); ++pos; }
-      if ((hits >> (4 * j)) & 4u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].z), first + 2); ++pos; }
-      if ((hits >> (4 * j)) & 8u) { if (pos < cap) list[pos] = make_comp(key_of(v[j].w), first + 3); ++pos; }
+    if (lane == 0) base = atomicAdd(counter, total);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    int pos = base + before;
+    while (hits != 0u) {
+      const int e = __ffs(hits) - 1;
+      hits &= hits - 1u;
+      const int lu = static_cast<int>(threadIdx.x) + (e >> 2) * kThreads;
+      float x;
+      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 4u * (e & 3)));
+      if (pos < cap) list[pos] = make_comp(key_of(x), 4 * (first_unit + lu) - mis + (e & 3));
+      ++pos;
     }
   }
 }
@@ -581,9 +617,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   ts.src = reinterpret_cast<const float4*>(chunk.abase) + chunk.fb;
   ts.ring = smem_addr(smem + kSmemRing);
   ts.bars = smem_addr(&sh.bars[0]);
+  ts.ebars = smem_addr(&sh.ebars[0]);
   ts.n_units = chunk.fe - chunk.fb;
   ts.n_tiles = (ts.n_units + kTileUnits - 1) / kTileUnits;
-  ts.stages = p.ring_stages;
   ts.timed_out = false;
   if (tid == 0) {
     sh.stage_count = 0;
@@ -592,7 +628,10 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     sh.small_count = 0;
     sh.big_count = 0;
     if (!HAS_MAP) {
-      for (int s = 0; s < ts.stages; ++s) mbar_init(ts.bars + 8u * s, 1u);
+      for (int s = 0; s < kStages; ++s) {
+        mbar_init(ts.bars + 8u * s, 1u);
+        mbar_init(ts.ebars + 8u * s, kWarps);
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
@@ -604,7 +643,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   } else {
     stream_forward(ts, [&](uint32_t tile, int, int units) {
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
+      for (int j = 0; j < kTileUnits / kThreads; ++j) {
         const int lu = tid + j * kThreads;
         if (lu < units) {
           const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
@@ -657,7 +696,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     }
     __syncthreads();
 
-    FF_TRACE(p, 16);
     LevelCtx ctx;
     ctx.Pn = Pn;
     ctx.Pmax = Pmax;
@@ -680,7 +718,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
       const int cap = final_level ? kSortCap : kCandCap;
       stream_again(ts, [&](uint32_t tile, int tt, int units) {
         collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, list, cap, counter);
-        if (tt < 8) FF_TRACE(p, 8 + tt);
       });
       float x = 0.f;
       const int pos = partial_element(chunk, x);
