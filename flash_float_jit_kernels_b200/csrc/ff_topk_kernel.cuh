@@ -325,8 +325,8 @@ struct ClusterShared {
   int sort_count;
   int cand_count;
   int push_base;
-  int small_count;
-  int big_count;
+  int small_count;   // ranking units queued in the finish
+  int big_count;     // elements of large buckets queued in the finish
   unsigned long long bars[kMaxStages + 1];
   unsigned long long ebars[kMaxStages + 1];
 };
@@ -626,7 +626,6 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     sh.sort_count = 0;
     sh.cand_count = 0;
     sh.small_count = 0;
-    sh.big_count = 0;
     if (!HAS_MAP) {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(ts.bars + 8u * s, 1u);
@@ -819,39 +818,67 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   // A counting sort on an adaptive linear digit: bin = (comp - floor) >> shift
   // with shift chosen so the survivors' composite range spans <= 4096 bins (any
   // monotone bin map keeps the result exact).  Every CTA builds the same
-  // buckets from its copy of the survivor list, each thread holding up to 8
-  // survivors in registers.  A survivor alone in its bucket is placed at once;
-  // the others are ranked inside their bucket by counting, and that work is
-  // shared out over the cluster by element: small buckets by one thread per
-  // element, large ones (heavy ties) by 8 lanes per element.
-  constexpr int kPer = kSortCap / kThreads;
-  uint32_t* bucket_start = reinterpret_cast<uint32_t*>(smem + kSmemCand);        // #(bin > b)
+  // buckets from its copy of the survivor list.  The exact rank inside a bucket
+  // is found by counting, cut into units of (element, 16 bucket entries) that
+  // are spread over all threads, and that work is shared out over the cluster
+  // by element.  The loops are deliberately not unrolled: this code runs once
+  // per row and its instruction footprint costs more than its trip counts.
+  uint32_t* E = reinterpret_cast<uint32_t*>(smem + kSmemCand);                     // #(bin > b), padded index
   uint64_t* bucketed = stage;
-  ulonglong2* small_list = reinterpret_cast<ulonglong2*>(smem + kSmemRing);        // kSortCap x 16 B
-  int* big_list = reinterpret_cast<int*>(smem + kSmemRing + kSortCap * 16);        // kSortCap x 4 B
-  uint64_t e[kPer];
-  uint32_t hmax = 0u;
-#pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    const int i = tid + j * kThreads;
-    e[j] = i < T ? sortbuf[i] : 0ull;
-    hmax = max(hmax, static_cast<uint32_t>(e[j] >> 32));
+  uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing);                     // bucket sizes, padded index
+  uint16_t* at_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 20 * 1024);     // slot of survivor i
+  uint32_t* rankcnt = reinterpret_cast<uint32_t*>(smem + kSmemRing + 28 * 1024);    // per slot: #greater in bucket
+  uint32_t* units = reinterpret_cast<uint32_t*>(smem + kSmemRing + 44 * 1024);      // (slot << 8) | chunk, <= 8192
+  auto pad = [](uint32_t b) { return b + (b >> 3); };   // 8 consecutive bins per thread -> distinct banks
+  constexpr int kPadBins = kMaxBins + kMaxBins / 8;
+  // bounds of the survivors' composites: exact on the key half, and exact on the
+  // index half too when every key is equal (then only the indices separate them)
+  uint32_t hmax = 0u, hmin = 0xffffffffu, lmax = 0u, lmin = 0xffffffffu;
+#pragma unroll 1
+  for (int i = tid; i < T; i += kThreads) {
+    const uint64_t c = sortbuf[i];
+    hmax = max(hmax, static_cast<uint32_t>(c >> 32));
+    hmin = min(hmin, static_cast<uint32_t>(c >> 32));
+    lmax = max(lmax, static_cast<uint32_t>(c));
+    lmin = min(lmin, static_cast<uint32_t>(c));
   }
   hmax = __reduce_max_sync(0xffffffffu, hmax);
-  if ((tid & 31) == 0) sh.warp_tot[tid >> 5] = static_cast<int>(hmax);
-  for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
+  hmin = __reduce_min_sync(0xffffffffu, hmin);
+  lmax = __reduce_max_sync(0xffffffffu, lmax);
+  lmin = __reduce_min_sync(0xffffffffu, lmin);
+  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 76 * 1024);   // 4 x kWarps words
+  if ((tid & 31) == 0) {
+    red4[tid >> 5] = hmax;
+    red4[kWarps + (tid >> 5)] = hmin;
+    red4[2 * kWarps + (tid >> 5)] = lmax;
+    red4[3 * kWarps + (tid >> 5)] = lmin;
+  }
+#pragma unroll 1
+  for (int i = tid; i < kPadBins; i += kThreads) fh[i] = 0u;
+#pragma unroll 1
+  for (int i = tid; i < T; i += kThreads) rankcnt[i] = 0u;
+  if (tid == 0) {
+    sh.small_count = 0;
+    sh.big_count = 0;
+  }
   __syncthreads();
 #pragma unroll
-  for (int w = 0; w < kWarps; ++w) hmax = max(hmax, static_cast<uint32_t>(sh.warp_tot[w]));
-  const uint64_t lo = floor_comp;
-  const uint64_t span = ((static_cast<uint64_t>(hmax) << 32) | 0xffffffffull) - lo;
+  for (int w = 0; w < kWarps; ++w) {
+    hmax = max(hmax, red4[w]);
+    hmin = min(hmin, red4[kWarps + w]);
+    lmax = max(lmax, red4[2 * kWarps + w]);
+    lmin = min(lmin, red4[3 * kWarps + w]);
+  }
+  const bool one_key = hmax == hmin;
+  const uint64_t lo = (static_cast<uint64_t>(hmin) << 32) | (one_key ? lmin : 0u);
+  const uint64_t span = ((static_cast<uint64_t>(hmax) << 32) | (one_key ? lmax : 0xffffffffu)) - lo;
   const int nbits = span == 0ull ? 0 : 64 - __clzll(static_cast<long long>(span));
   const int bshift = nbits > 12 ? nbits - 12 : 0;
-  uint32_t bin[kPer];
-#pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    bin[j] = static_cast<uint32_t>((e[j] - lo) >> bshift);
-    if (tid + j * kThreads < T) atomicAdd(&hist[bin[j]], 1u);
+  // arrival order inside the bin doubles as the scatter offset
+#pragma unroll 1
+  for (int i = tid; i < T; i += kThreads) {
+    const uint32_t b = static_cast<uint32_t>((sortbuf[i] - lo) >> bshift);
+    at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
   }
   __syncthreads();
   FF_TRACE(p, 22);
@@ -859,98 +886,97 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     constexpr int per = kMaxBins / kThreads;
     int local = 0;
 #pragma unroll
-    for (int q = 0; q < per; ++q) local += static_cast<int>(hist[tid * per + q]);
+    for (int q = 0; q < per; ++q) local += static_cast<int>(fh[pad(tid * per + q)]);
     int total;
     int running = block_suffix_exclusive(local, sh.warp_tot, total);
 #pragma unroll
     for (int q = per - 1; q >= 0; --q) {
-      const int b = tid * per + q;
-      bucket_start[b] = static_cast<uint32_t>(running);
-      running += static_cast<int>(hist[b]);
-      hist[b] = 0u;   // becomes the scatter cursor
+      const uint32_t b = pad(tid * per + q);
+      E[b] = static_cast<uint32_t>(running);
+      running += static_cast<int>(fh[b]);
     }
   }
   __syncthreads();
   FF_TRACE(p, 23);
-  uint32_t begin[kPer], at[kPer];   // bucket start and slot of e[j] in the bucketed array
-#pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    if (tid + j * kThreads < T) {
-      begin[j] = bucket_start[bin[j]];
-      at[j] = begin[j] + atomicAdd(&hist[bin[j]], 1u);
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    if (tid + j * kThreads < T) bucketed[at[j]] = e[j];
+#pragma unroll 1
+  for (int i = tid; i < T; i += kThreads) {
+    const uint64_t c = sortbuf[i];
+    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+    const uint32_t at = E[b] + at_arr[i];
+    at_arr[i] = static_cast<uint16_t>(at);
+    bucketed[at] = c;
   }
   __syncthreads();
   FF_TRACE(p, 24);
-  // Scatter order inside a bucket differs from CTA to CTA (atomics), so the
-  // ranking work is shared out by element identity, not by array position.
-  constexpr int kSmallBucket = 8;
-#pragma unroll
-  for (int j = 0; j < kPer; ++j) {
-    if (tid + j * kThreads >= T) continue;
-    const uint64_t c = e[j];
-    if (static_cast<int>(begin[j]) >= k) continue;
-    if ((static_cast<uint32_t>(c) & static_cast<uint32_t>(C - 1)) != static_cast<uint32_t>(rank)) continue;
-    const uint32_t n_b = hist[bin[j]];
-    if (n_b == 1u) {
-      emit(p, row, static_cast<int>(begin[j]), c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
-    } else if (n_b <= kSmallBucket) {
-      const int slot = atomicAdd(&sh.small_count, 1);
-      small_list[slot] = make_ulonglong2(c, static_cast<uint64_t>(at[j]) | (static_cast<uint64_t>(begin[j]) << 16) |
-                                                (static_cast<uint64_t>(n_b) << 32));
+  // The survivor list has the same order in every CTA (the bucketed array does
+  // not: atomics), so the ranking work is shared out by list index: CTA `rank`
+  // owns the survivors i with i % C == rank.  Buckets of up to kUnitBucket
+  // entries are cut into units of 16 entries; larger ones (many equal keys next
+  // to a far outlier) are scanned by a whole warp per element.
+  constexpr uint32_t kUnitBucket = 32u;
+  uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 78 * 1024);   // slots, <= kSortCap
+#pragma unroll 1
+  for (int i = tid * C + rank; i < T; i += kThreads * C) {
+    const uint64_t c = sortbuf[i];
+    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+    if (static_cast<int>(E[b]) >= k) continue;
+    const uint32_t n_b = fh[b];
+    if (n_b <= 1u) continue;
+    if (n_b <= kUnitBucket) {
+      const int nu = static_cast<int>((n_b + 15u) >> 4);
+      const int base = atomicAdd(&sh.small_count, nu);
+      for (int u = 0; u < nu; ++u) units[base + u] = (static_cast<uint32_t>(at_arr[i]) << 8) | static_cast<uint32_t>(u);
     } else {
-      big_list[atomicAdd(&sh.big_count, 1)] = static_cast<int>(at[j]);
+      big_list[atomicAdd(&sh.big_count, 1)] = at_arr[i];
     }
   }
-  FF_TRACE(p, 31);
   __syncthreads();
+  FF_TRACE(p, 31);
   {
-    const int n_small = sh.small_count;
-    for (int i = tid; i < n_small; i += kThreads) {
-      const ulonglong2 it = small_list[i];
-      const uint64_t c = it.x;
-      const int me = static_cast<int>(it.y & 0xffffu);
-      const int b0 = static_cast<int>((it.y >> 16) & 0xffffu);
-      const int n_b = static_cast<int>(it.y >> 32);
-      int pos = b0;
-#pragma unroll
-      for (int q = 0; q < kSmallBucket; ++q) {
-        if (q < n_b) {
-          const uint64_t o = bucketed[b0 + q];
-          pos += (o > c || (o == c && b0 + q < me)) ? 1 : 0;
-        }
+    const int n_units = sh.small_count;
+#pragma unroll 1
+    for (int ui = tid; ui < n_units; ui += kThreads) {
+      const uint32_t un = units[ui];
+      const int me = static_cast<int>(un >> 8);
+      const uint64_t c = bucketed[me];
+      const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+      const int b0 = static_cast<int>(E[b]);
+      const int q0 = b0 + 16 * static_cast<int>(un & 0xffu);
+      const int q1 = min(b0 + static_cast<int>(fh[b]), q0 + 16);
+      uint32_t cnt = 0;
+#pragma unroll 4
+      for (int q = q0; q < q1; ++q) {
+        const uint64_t o = bucketed[q];
+        cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
       }
-      if (pos < k) emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+      if (cnt != 0u) atomicAdd(&rankcnt[me], cnt);
+    }
+    const int n_big = sh.big_count;
+    const int lane = tid & 31;
+#pragma unroll 1
+    for (int d = tid >> 5; d < n_big; d += kWarps) {   // uniform per warp
+      const int me = big_list[d];
+      const uint64_t c = bucketed[me];
+      const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+      const int b0 = static_cast<int>(E[b]);
+      const int q1 = b0 + static_cast<int>(fh[b]);
+      uint32_t cnt = 0;
+#pragma unroll 2
+      for (int q = b0 + lane; q < q1; q += 32) {
+        const uint64_t o = bucketed[q];
+        cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
+      }
+      cnt = __reduce_add_sync(0xffffffffu, cnt);
+      if (lane == 0) rankcnt[me] = cnt;
     }
   }
-  {
-    const int n_big = sh.big_count;
-    const int group = tid >> 3, sub = tid & 7;
-    // the trip count is uniform over the CTA so every lane reaches the shuffles
-    for (int d0 = 0; d0 < n_big; d0 += kThreads / 8) {
-      const int d = d0 + group;
-      const bool active = d < n_big;
-      const int me = active ? big_list[d] : 0;
-      const uint64_t c = bucketed[me];
-      const uint32_t b = static_cast<uint32_t>((c - lo) >> bshift);
-      const int b0 = static_cast<int>(bucket_start[b]);
-      const int end = active ? b0 + static_cast<int>(hist[b]) : b0;
-      int cnt = 0;
-      for (int q = b0 + sub; q < end; q += 8) {
-        const uint64_t o = bucketed[q];
-        cnt += (o > c || (o == c && q < me)) ? 1 : 0;
-      }
-      cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
-      cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
-      cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
-      const int pos = b0 + cnt;
-      if (active && sub == 0 && pos < k)
-        emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
-    }
+  __syncthreads();
+#pragma unroll 1
+  for (int i = tid * C + rank; i < T; i += kThreads * C) {
+    const uint64_t c = sortbuf[i];
+    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+    const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
+    if (pos < k) emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
   }
   FF_TRACE(p, 25);
 }
