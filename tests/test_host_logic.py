@@ -43,3 +43,16 @@ def test_shard_bounds_partition_the_row(L, P):
 def test_shard_bounds_rejects_bad_rank():
     with pytest.raises(TopkArgumentError):
         shard_bounds(100, 4, 4)
+
+
+def test_reference_import_path_shim(monkeypatch):
+    import sys
+    from pathlib import Path
+    import flash_float_jit_kernels_b200 as pkg
+    monkeypatch.syspath_prepend(str(Path(pkg.__file__).parent / "compat"))
+    sys.modules.pop("jit_kernel", None)
+    sys.modules.pop("jit_kernel.topk_indexer", None)
+    from jit_kernel.topk_indexer import fast_topk_v3 as shim
+    assert shim is pkg.fast_topk_v3
+    sys.modules.pop("jit_kernel", None)
+    sys.modules.pop("jit_kernel.topk_indexer", None)
