@@ -20,6 +20,7 @@ SIGNATURES = {
     "ff_topk_init": (c_int, [c_int]),
     "ff_topk_set_cluster_override": (c_int, [c_int32]),
     "ff_topk_set_trace_buffer": (c_int, [c_void_p]),
+    "ff_topk_set_groups_override": (c_int, [c_int32]),
     "ff_topk_policy_cluster_size": (c_int32, [c_int32, c_int64, c_int32]),
     "ff_topk_workspace_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "ff_topk_launch": (

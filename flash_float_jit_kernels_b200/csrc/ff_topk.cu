@@ -16,6 +16,7 @@ namespace {
 thread_local char g_err[256] = "";
 std::atomic<int64_t> g_launches{0};
 std::atomic<int> g_cluster_override{0};
+std::atomic<int> g_groups_override{0};
 std::atomic<unsigned long long*> g_trace{nullptr};
 
 constexpr int kMaxDevices = 64;
@@ -23,6 +24,7 @@ std::once_flag g_init_once[kMaxDevices];
 int g_init_rc[kMaxDevices];
 int g_max_cluster[kMaxDevices];  // largest schedulable cluster size per device
 int g_sm_count[kMaxDevices];
+int g_active_clusters[kMaxDevices][5];  // co-resident clusters of size 1, 2, 4, 8, 16
 
 int fail(int code, const char* msg) {
   snprintf(g_err, sizeof(g_err), "%s", msg);
@@ -39,6 +41,27 @@ cudaError_t prepare_kernel(K kernel) {
                                        ff::smem_bytes_for(ff::kMaxStages));
   if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+}
+
+template <typename K>
+int active_clusters_for(K kernel, int c) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(c, 1, 1);
+  cfg.blockDim = dim3(ff::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = c;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return n;
 }
 
 template <typename K>
@@ -71,6 +94,8 @@ void init_device(int device) {
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true>);
   if (e == cudaSuccess) {
     g_max_cluster[device] = max_cluster_for(ff::topk_cluster_kernel<false>);
+    for (int i = 0; i < 5; ++i)
+      g_active_clusters[device][i] = active_clusters_for(ff::topk_cluster_kernel<false>, 1 << i);
     int sms = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     g_sm_count[device] = sms > 0 ? sms : 148;
@@ -121,20 +146,53 @@ int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
   return c;
 }
 
+// Rows that are long and few are split over several clusters (groups) so that
+// all SMs sweep them; that needs the caller's zero-filled workspace and a
+// cooperative launch (all CTAs of a row wait for each other through global
+// memory).  Returns the number of clusters per row and may lower `cluster`.
+constexpr int64_t kGroupMinWidth = 524288;
+constexpr int kGroupCluster = 8;
+int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes, int* cluster) {
+  int g = g_groups_override.load();
+  if (g == 0) {
+    const char* env = getenv("FF_TOPK_GROUPS");
+    if (env != nullptr) g = atoi(env);
+  }
+  const size_t need = static_cast<size_t>(B) * ff::kWsRowWords * sizeof(uint32_t);
+  if (workspace_bytes < need || g == 1) return 1;
+  int c = *cluster;
+  if (g == 0) {
+    if (L_width < kGroupMinWidth || g_cluster_override.load() != 0) return 1;
+    c = kGroupCluster;
+    g = static_cast<int>((L_width + c * 8192 - 1) / (static_cast<int64_t>(c) * 8192));   // one 32 KiB tile per CTA
+  }
+  int log2c = 0;
+  while ((1 << log2c) < c) ++log2c;
+  const int room = g_active_clusters[device][log2c] / (B > 0 ? B : 1);   // co-resident clusters per row
+  if (g > room) g = room;
+  if (g > 64) g = 64;
+  if (g < 2) return 1;
+  *cluster = c;
+  return g;
+}
+
 template <bool HAS_MAP>
 int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(p.B) * cluster, 1, 1);
+  const int groups = p.groups > 1 ? p.groups : 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(p.B) * cluster * groups, 1, 1);
   cfg.blockDim = dim3(ff::kThreads, 1, 1);
   cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;
+  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = groups > 1 ? 2 : 1;
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
 
@@ -190,9 +248,15 @@ int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k) {
 }
 
 size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
-  (void)B;
-  (void)L_width;
   (void)k;
+  // Only rows split over several clusters use scratch: long rows, small batches.
+  if (B < 1 || B > 16 || (L_width < kGroupMinWidth && g_groups_override.load() < 2)) return 0;
+  return static_cast<size_t>(B) * ff::kWsRowWords * sizeof(uint32_t);
+}
+
+int ff_topk_set_groups_override(int32_t g) {
+  if (g < 0 || g > 64) return fail(FF_ERR_BAD_CLUSTER, "groups override must be in [0, 64]");
+  g_groups_override.store(g);
   return 0;
 }
 
@@ -202,8 +266,6 @@ int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int3
                              int64_t table_stride, const int32_t* cu_seqlens_q,
                              int32_t n_table_rows, const int32_t* offsets, void* workspace,
                              size_t workspace_bytes, int32_t* status, void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   int rc = check_common(B, L_width, k);
   if (rc != 0) return rc;
   if (B == 0) return 0;
@@ -241,7 +303,12 @@ int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int3
   p.n_table_rows = n_table_rows;
   p.offsets = offsets;
   p.status = status;
-  return launch<false>(p, choose_cluster(device, B, L_width, k), static_cast<cudaStream_t>(stream));
+  int cluster = choose_cluster(device, B, L_width, k);
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
+    p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster);
+    p.workspace = static_cast<uint32_t*>(workspace);
+  }
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
 }
 
 int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
@@ -257,8 +324,6 @@ int ff_topk_cp_local(const float* scores, int64_t row_stride, const int32_t* len
                      int32_t* cand_idx, float* cand_val, int32_t B, int64_t L_width, int32_t k,
                      int64_t shard_offset, void* workspace, size_t workspace_bytes,
                      int32_t* status, void* stream) {
-  (void)workspace;
-  (void)workspace_bytes;
   int rc = check_common(B, L_width, k);
   if (rc != 0) return rc;
   if (B == 0) return 0;
@@ -282,7 +347,12 @@ int ff_topk_cp_local(const float* scores, int64_t row_stride, const int32_t* len
   p.shard_offset = shard_offset;
   p.fixed_len = -1;
   p.status = status;
-  return launch<false>(p, choose_cluster(device, B, L_width, k), static_cast<cudaStream_t>(stream));
+  int cluster = choose_cluster(device, B, L_width, k);
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
+    p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster);
+    p.workspace = static_cast<uint32_t*>(workspace);
+  }
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
 }
 
 int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_ranks,

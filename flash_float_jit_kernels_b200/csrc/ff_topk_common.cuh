@@ -74,6 +74,8 @@ struct TopkParams {
   int32_t n_table_rows;
   const int32_t* offsets;      // [B] ragged offsets
   int32_t* status;             // optional soft-error word
+  int32_t groups;              // clusters per row (> 1 needs workspace and a cooperative launch)
+  uint32_t* workspace;         // zero-filled global scratch, kWsRowWords words per row
   unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
 

@@ -326,6 +326,7 @@ struct ClusterShared {
   int cand_count;
   int push_base;
   int small_count;   // ranking units queued in the finish
+  int flag;          // row-barrier result / last-CTA flag
   int big_count;     // elements of large buckets queued in the finish
   unsigned long long bars[kMaxStages + 1];
   unsigned long long ebars[kMaxStages + 1];
@@ -426,6 +427,42 @@ __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first
   }
 }
 
+// ---- rows split over several clusters: global scratch and row-wide barriers ----
+// Per-row scratch in global memory (all zero between launches; the kernel
+// leaves it zeroed).  Word offsets:
+//   [0, 6)   arrivals at the histogram barrier of digit level 0..5
+//   [6]      arrivals at the survivor barrier      [7] CTAs that are done
+//   [8]      survivors appended so far
+//   [64, 64 + 6 * 4096)          one 4096-bin global histogram per digit level
+//   [64 + 6 * 4096, + 2 * 4096)  survivor list (4096 x 64-bit composites)
+constexpr int kWsHeaderWords = 64;
+constexpr int kWsHistWords = kNumLevels * kMaxBins;
+constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kSortCap;
+constexpr int kSpinLimit = 1 << 21;   // bounded polling of a row barrier (about a second)
+
+// All `expected` CTAs of a row meet here (they are co-resident: cooperative
+// launch).  Thread 0 publishes this CTA's earlier global writes and polls the
+// arrival counter; returns false if the poll limit ran out.
+__device__ __forceinline__ bool row_barrier(uint32_t* counter, uint32_t expected, int* flag) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    int ok = 0;
+    for (int i = 0; i < kSpinLimit; ++i) {
+      uint32_t v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= expected) {
+        ok = 1;
+        break;
+      }
+    }
+    *flag = ok;
+  }
+  __syncthreads();
+  return *flag != 0;
+}
+
 // Cluster-wide histogram merge (reduce-scatter over distributed shared memory)
 // and suffix scan over the per-CTA slices.  On return every CTA's sh.res holds
 // the digit t with  #(digit > t) < r <= #(digit >= t), and those two counts.
@@ -433,10 +470,11 @@ __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first
 // `merged` must not alias `hist`; with a single CTA the histogram is scanned in place.
 __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C, int rank,
                                                uint32_t* hist, uint32_t* merged, int nbins, int r,
-                                               bool raw0, ClusterShared& sh, const TopkParams& p, bool tr) {
+                                               bool raw0, ClusterShared& sh, const TopkParams& p, bool tr,
+                                               int G, uint32_t* ws, int level, bool& timed_out) {
   const int tid = threadIdx.x;
-  const int slice_n = nbins / C;
-  const int slice_base = rank * slice_n;
+  int slice_n = nbins / C;
+  int slice_base = rank * slice_n;
   if (C > 1) {
     for (int i = tid; i < slice_n; i += kThreads) merged[i] = 0u;
   }
@@ -469,10 +507,28 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   }
   if (tr) FF_TRACE(p, 27);
   // slice value i: merged[i], or (single CTA) the histogram itself in monotone order
+  bool from_merged = C > 1;
   auto slice_at = [&](int i) -> int {
-    if (C > 1) return static_cast<int>(merged[i]);
+    if (from_merged) return static_cast<int>(merged[i]);
     return static_cast<int>(hist[raw0 ? raw_of_bin(i) : i]);
   };
+  if (G > 1) {
+    // Cross-cluster step: the cluster's merged slices are added into the row's
+    // global histogram (L2 atomics carry only the G-way part of the merge), all
+    // CTAs of the row meet, and every CTA reads the whole histogram back.
+    uint32_t* gh = ws + kWsHeaderWords + level * kMaxBins;
+    for (int i = tid; i < slice_n; i += kThreads) {
+      const int v = slice_at(i);
+      if (v != 0) atomicAdd(&gh[slice_base + i], static_cast<uint32_t>(v));
+    }
+    if (!row_barrier(ws + level, static_cast<uint32_t>(G * C), &sh.flag)) timed_out = true;
+    for (int i = tid; i < nbins; i += kThreads) merged[i] = __ldcg(&gh[i]);
+    __syncthreads();
+    from_merged = true;
+    slice_n = nbins;
+    slice_base = 0;
+  }
+  const bool publish_remote = C > 1 && G == 1;
   const int per = slice_n >= kThreads ? slice_n / kThreads : 1;
   const int first = tid * per;
   int local = 0;
@@ -482,13 +538,15 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   int total;
   const int excl = block_suffix_exclusive(local, sh.warp_tot, total);
   if (tr) FF_TRACE(p, 28);
-  if (C > 1) {
+  if (publish_remote) {
     if (tid < C) dsmem_st_u32(dsmem_addr(smem_addr(&sh.slice_tot[rank]), tid), static_cast<uint32_t>(total));
     cluster.sync();  // slice totals of every CTA have arrived
   }
   if (tr) FF_TRACE(p, 29);
   int above_slice = 0;
-  for (int c = rank + 1; c < C; ++c) above_slice += sh.slice_tot[c];
+  if (publish_remote) {
+    for (int c = rank + 1; c < C; ++c) above_slice += sh.slice_tot[c];
+  }
   if (first < slice_n) {
     int running = above_slice + excl;
     for (int e = per - 1; e >= 0; --e) {
@@ -496,7 +554,7 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
       const int next = running;
       running += cnt;
       if (next < r && r <= running) {
-        if (C > 1) {
+        if (publish_remote) {
           for (int c = 0; c < C; ++c) {
             const uint32_t a = dsmem_addr(smem_addr(&sh.res[0]), c);
             dsmem_st_u32(a + 4, static_cast<uint32_t>(next));
@@ -512,7 +570,7 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
     }
   }
   if (tr) FF_TRACE(p, 30);
-  if (C > 1) cluster.sync(); else __syncthreads();   // the threshold triple has arrived everywhere
+  if (publish_remote) cluster.sync(); else __syncthreads();   // the threshold triple has arrived everywhere
 }
 
 // Writes output slot j of `row` from a window-relative index (or -1) and key.
@@ -555,7 +613,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   cg::cluster_group cluster = cg::this_cluster();
   const int C = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());
-  const int row = static_cast<int>(blockIdx.x) / C;
+  const int G = HAS_MAP ? 1 : max(p.groups, 1);       // clusters per row
+  const int row = static_cast<int>(blockIdx.x) / (C * G);
+  const int group = (static_cast<int>(blockIdx.x) / C) % G;
+  const int n_share = C * G;                           // CTAs working on this row
+  const int my_share = group * C + rank;
+  uint32_t* ws = G > 1 ? p.workspace + static_cast<size_t>(row) * kWsRowWords : nullptr;
   const int tid = threadIdx.x;
   const int k = p.k;
 
@@ -590,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   // ---- short rows: nothing to select --------------------------------------
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
   if (identity || len <= k) {
-    if (rank != 0) return;
+    if (my_share != 0) return;
     for (int j = tid; j < k; j += kThreads) {
       if (HAS_MAP && !identity) {
         // no more candidates than k slots: pass them through in position order
@@ -608,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     return;
   }
 
-  const Chunk chunk = make_chunk(rowp, imap, len, C, rank, p.seg_len, p.seg_stride);
+  const Chunk chunk = make_chunk(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
 
   // ---- level 0: 12-bit histogram of the whole chunk -----------------------
@@ -665,6 +728,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   int cand_n = 0;
   bool ok = true;
   int expected_total = 0;
+  int levels_used = 0;
   uint64_t floor_comp = 0;  // no survivor's composite is below this
 
 #pragma unroll 1
@@ -672,7 +736,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     const int bits = level_bits(level);
     const int shift = level_shift(level);
     const bool raw0 = !HAS_MAP && level == 0;
-    merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0);
+    merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0, G, ws, level,
+                   ts.timed_out);
+    levels_used = level + 1;
     FF_TRACE(p, 2 + 3 * level);
     const int t = sh.res[0];
     const int above = sh.res[1];
@@ -759,7 +825,16 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     // coalesced remote stores fill it.  Each CTA ends up with the full list and
     // can take a share of the finishing work without further exchange.
     const int n_stage = min(sh.stage_count, kSortCap);
-    if (n_stage > 0) {
+    if (n_stage > 0 && G > 1) {
+      // rows split over clusters: the survivor list lives in global scratch
+      if (tid == 0) sh.push_base = static_cast<int>(atomicAdd(ws + 8, static_cast<uint32_t>(n_stage)));
+      __syncthreads();
+      uint64_t* gsurv = reinterpret_cast<uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+      const int base = sh.push_base;
+      for (int i = tid; i < n_stage; i += kThreads) {
+        if (base + i < kSortCap) gsurv[base + i] = stage[i];
+      }
+    } else if (n_stage > 0) {
       if (C == 1) {
         const int base = sh.sort_count;
         __syncthreads();
@@ -799,19 +874,39 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     P = Pn;
   }
 
-  if (C > 1) cluster.sync(); else __syncthreads();   // every survivor has landed in every CTA's list
+  if (G > 1) {
+    if (!row_barrier(ws + 6, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
+    const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+    const int n_load = ok ? min(expected_total, kSortCap) : 0;
+    for (int i = tid; i < n_load; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
+    if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));
+    __syncthreads();
+    // Last use of the scratch: the CTA that counts in last zeroes it for the next launch.
+    if (tid == 0) {
+      __threadfence();
+      sh.flag = atomicAdd(ws + 7, 1u) == static_cast<uint32_t>(n_share - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (sh.flag) {
+      for (int i = tid; i < kWsHeaderWords + levels_used * kMaxBins; i += kThreads) ws[i] = 0u;
+    }
+  } else if (C > 1) {
+    cluster.sync();   // every survivor has landed in every CTA's list
+  } else {
+    __syncthreads();
+  }
   FF_TRACE(p, 20);
 
   if (ts.timed_out && p.status != nullptr && tid == 0) atomicOr(p.status, 2);
   if (!ok) {
-    if (p.status != nullptr && tid == 0 && rank == 0) atomicOr(p.status, 4);
-    if (rank == 0) {
+    if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
+    if (my_share == 0) {
       for (int j = tid; j < k; j += kThreads) emit(p, row, j, -1, 0u, HAS_MAP, table_row);
     }
     return;
   }
   const int T = min(expected_total, kSortCap);
-  if (rank == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
+  if (my_share == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
     atomicOr(p.status, 1);
 
   // ---- finish: rank the T survivors and write the first k ------------------
@@ -909,14 +1004,14 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   __syncthreads();
   FF_TRACE(p, 24);
   // The survivor list has the same order in every CTA (the bucketed array does
-  // not: atomics), so the ranking work is shared out by list index: CTA `rank`
-  // owns the survivors i with i % C == rank.  Buckets of up to kUnitBucket
+  // not: atomics), so the ranking work is shared out by list index: CTA number s of the
+  // n CTAs working on the row owns the survivors i with i % n == s.  Buckets of up to kUnitBucket
   // entries are cut into units of 16 entries; larger ones (many equal keys next
   // to a far outlier) are scanned by a whole warp per element.
   constexpr uint32_t kUnitBucket = 32u;
   uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 78 * 1024);   // slots, <= kSortCap
 #pragma unroll 1
-  for (int i = tid * C + rank; i < T; i += kThreads * C) {
+  for (int i = tid * n_share + my_share; i < T; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     if (static_cast<int>(E[b]) >= k) continue;
@@ -972,7 +1067,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   }
   __syncthreads();
 #pragma unroll 1
-  for (int i = tid * C + rank; i < T; i += kThreads * C) {
+  for (int i = tid * n_share + my_share; i < T; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);

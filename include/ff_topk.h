@@ -58,10 +58,12 @@ extern "C" {
  * (topk_indexer_radix.cu:1195-1233). */
 int ff_topk_init(int device);
 
-/* Bytes of caller-owned scratch ff_topk_launch needs for (B, L_width, k).
+/* Bytes of caller-owned scratch ff_topk_launch can use for (B, L_width, k).
  * The workspace must be 256-byte aligned, zero-filled once before first use
  * (the kernels leave it zeroed), and must not be shared by launches that can
- * overlap on the GPU.  May return 0 when the chosen kernel needs none. */
+ * overlap on the GPU.  Returns 0 when no scratch is used (short rows or large
+ * batches).  Scratch is optional: without it (NULL / too small) long rows are
+ * handled by one cluster instead of being split over several. */
 size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k);
 
 /* The fast_topk_v3 hot path.  Replaces the TVM-FFI symbol `fast_topk`
@@ -129,6 +131,11 @@ int ff_topk_set_cluster_override(int32_t cluster_size);
  * pass NULL to switch tracing off.  Plays the role of the reference's
  * SMALL_K_PROFILE clock64 brackets (top_small_k.cuh:39-41,132-135). */
 int ff_topk_set_trace_buffer(void* device_buffer);
+
+/* Test / tuning hook: clusters per row (0 = automatic, 1 = never split a row,
+ * 2..64 = split every row with enough workspace over that many clusters of the
+ * current cluster size, clamped to what can be co-resident).  Process-wide. */
+int ff_topk_set_groups_override(int32_t groups);
 
 /* The cluster size the automatic policy picks for (B, L_width, k) on the
  * current device (after overrides). */

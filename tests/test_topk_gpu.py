@@ -246,3 +246,55 @@ def test_transform_page_table_and_ragged(ff, oracle):
     off = torch.tensor([0, 20000, 21000, 40999, 43047, 45096], dtype=torch.int32)
     pkg.fast_topk_transform_ragged_fused(s.cuda(), l2.cuda(), dst, off.cuda(), rs.cuda())
     assert np.array_equal(dst.cpu().numpy(), oracle.transform_ragged(idx2, off.numpy()))
+
+
+# ---- rows split over several clusters (global scratch + row-wide barriers) ----------------
+def run_grouped(ff, oracle, s, lengths, k, cluster, groups, rs=None, repeat=2):
+    pkg, lib = ff
+    assert lib.ff_topk_set_cluster_override(cluster) == 0
+    assert lib.ff_topk_set_groups_override(groups) == 0
+    try:
+        sd, ld = s.cuda(), lengths.cuda()
+        rsd = None if rs is None else rs.cuda()
+        exp = oracle.topk_c(s.numpy(), lengths.numpy(), k, None if rs is None else rs.numpy())
+        for _ in range(repeat):                      # the scratch must come back zeroed
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            out = pkg.fast_topk_v3(sd, ld, k, rsd, status=status)
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            assert np.array_equal(out.cpu().numpy(), exp), f"cluster={cluster} groups={groups}"
+    finally:
+        lib.ff_topk_set_groups_override(0)
+        lib.ff_topk_set_cluster_override(0)
+
+
+@pytest.mark.parametrize("cluster,groups", [(1, 2), (2, 3), (4, 5), (8, 4), (8, 16), (16, 2), (1, 64)])
+def test_rows_split_over_clusters(ff, oracle, cluster, groups):
+    g = torch.Generator().manual_seed(41)
+    s = torch.randn((2, 300001), generator=g).to(torch.bfloat16).float()
+    lengths = torch.tensor([300001, 123457], dtype=torch.int32)
+    for k in (512, 2048):
+        run_grouped(ff, oracle, s, lengths, k, cluster, groups)
+
+
+def test_split_rows_automatic_policy_at_full_size(ff, oracle):
+    from flash_float_jit_kernels_b200 import workloads as W
+    for L in (1 << 20, 1 << 22):
+        s, l, _ = W.gaussian_bf16_ties(1, L, seed=43)
+        run_grouped(ff, oracle, s, l, 2048, 0, 0)
+    s, l, _ = W.gaussian_outliers(4, 1 << 20, seed=44)
+    run_grouped(ff, oracle, s, l, 512, 0, 0)
+
+
+@pytest.mark.parametrize("cluster,groups", [(8, 4), (2, 7)])
+def test_split_rows_deeper_levels_and_ties(ff, oracle, cluster, groups):
+    L = 400000
+    s = torch.empty((4, L))
+    s[0] = 1.25                                                    # every element in one bin, all levels
+    s[1] = torch.rand((L,), generator=torch.Generator().manual_seed(2)) * 255.0   # coarse bins: second level
+    s[2] = torch.arange(L, dtype=torch.float32)                    # all winners in the last chunk
+    s[3] = torch.randint(0, 3, (L,), generator=torch.Generator().manual_seed(3)).float()
+    lengths = torch.tensor([L, L, L, L - 5], dtype=torch.int32)
+    rs = torch.tensor([0, 1, 2, 3], dtype=torch.int32)
+    run_grouped(ff, oracle, s, lengths - 3, 2048, cluster, groups, rs)
+    run_grouped(ff, oracle, s, lengths, 7, cluster, groups)
