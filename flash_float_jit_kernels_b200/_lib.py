@@ -28,6 +28,10 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32,
          c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    "ff_topk_launch_static": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p],
+    ),
     "ff_topk_transform_launch": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int32,

@@ -202,6 +202,23 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   return 0;
 }
 
+// Built-in scratch for ff_topk_launch_static: enough for FF_TOPK_STATIC_MAX_ROWS
+// rows split over several clusters.  It lives in every GPU that loads this
+// library until the process exits.  In host code the name below is only a
+// handle for cudaGetSymbolAddress; it is never passed to a kernel.
+static __device__ __align__(256) uint32_t g_static_scratch[FF_TOPK_STATIC_MAX_ROWS * ff::kWsRowWords];
+std::once_flag g_static_once[kMaxDevices];
+int g_static_rc[kMaxDevices];
+uint32_t* g_static_ptr[kMaxDevices];
+
+// Runs once per device, with that device current.
+void resolve_static_scratch(int device) {
+  void* ptr = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+  g_static_rc[device] = static_cast<int>(e);
+  g_static_ptr[device] = e == cudaSuccess ? static_cast<uint32_t*>(ptr) : nullptr;
+}
+
 int check_common(int32_t B, int64_t L_width, int32_t k) {
   if (k < 1 || k > FF_TOPK_MAX_K) return fail(FF_ERR_BAD_K, "k must be in [1, 2048]");
   if (B < 0 || L_width < 0) return fail(FF_ERR_BAD_SHAPE, "negative B or L_width");
@@ -318,6 +335,48 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
   return ff_topk_transform_launch(scores, row_stride, lengths, row_starts, out_idx, B, L_width, k,
                                   FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, workspace,
                                   workspace_bytes, status, stream);
+}
+
+int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                          int32_t k, int32_t* status, void* stream) {
+  int rc = check_common(B, L_width, k);
+  if (rc != 0) return rc;
+  if (B > FF_TOPK_STATIC_MAX_ROWS)
+    return fail(FF_ERR_TOO_LARGE, "ff_topk_launch_static: B exceeds FF_TOPK_STATIC_MAX_ROWS rows of built-in scratch");
+  if (B == 0) return 0;
+  if (scores == nullptr || lengths == nullptr || out_idx == nullptr)
+    return fail(FF_ERR_NULL, "scores, lengths and out_idx must not be NULL");
+  if (row_stride < 0) return fail(FF_ERR_BAD_SHAPE, "negative row_stride");
+  if ((reinterpret_cast<uintptr_t>(scores) & 3u) != 0)
+    return fail(FF_ERR_BAD_SHAPE, "scores must be 4-byte aligned");
+  int device = 0;
+  rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  std::call_once(g_static_once[device], resolve_static_scratch, device);
+  if (g_static_rc[device] != 0 || g_static_ptr[device] == nullptr)
+    return fail_cuda(static_cast<cudaError_t>(g_static_rc[device]), "cudaGetSymbolAddress(built-in scratch)");
+  uint32_t* scratch = g_static_ptr[device];
+  const size_t row_bytes = static_cast<size_t>(ff::kWsRowWords) * sizeof(uint32_t);
+  // The array keeps whatever the previous call left; the counters and histograms must start at zero.
+  cudaError_t e = cudaMemsetAsync(scratch, 0, static_cast<size_t>(B) * row_bytes, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(built-in scratch)");
+  ff::TopkParams p = {};
+  p.scores = scores;
+  p.row_stride = row_stride;
+  p.lengths = lengths;
+  p.row_starts = row_starts;
+  p.out_idx = out_idx;
+  p.B = B;
+  p.k = k;
+  p.L_width = L_width;
+  p.fixed_len = -1;
+  p.epilogue = FF_EPILOGUE_INDEX;
+  p.status = status;
+  int cluster = choose_cluster(device, B, L_width, k);
+  p.groups = choose_groups(device, B, L_width, FF_TOPK_STATIC_MAX_ROWS * row_bytes, &cluster);
+  p.workspace = scratch;
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
 }
 
 int ff_topk_cp_local(const float* scores, int64_t row_stride, const int32_t* lengths,

@@ -81,6 +81,31 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
                    int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
                    void* stream);
 
+/* Same result as ff_topk_launch, for callers that cannot hand over scratch
+ * memory.  (No counterpart in the reference.)  Some hosts of this library may
+ * not allocate device memory at all: an operator plugged into a runtime that
+ * owns every buffer and gives a plugin only its inputs and outputs, a serving
+ * loop whose memory pool is frozen after warm-up, or code running where a
+ * cudaMalloc would stall the whole device.  Without a workspace ff_topk_launch
+ * still works but handles a long row with a single cluster; this entry point
+ * keeps the fast path (a long row split over several clusters) by using scratch
+ * built into the library: a zero-initialised __device__ array of
+ * FF_TOPK_STATIC_MAX_ROWS * 131,328 bytes (about 513 KiB) that every GPU
+ * loading the library holds until the process exits.
+ *   - B > FF_TOPK_STATIC_MAX_ROWS is rejected with FF_ERR_TOO_LARGE.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine; it
+ *     enqueues one cudaMemsetAsync (the scratch keeps the previous call's
+ *     contents and its counters must start at zero) and one kernel on `stream`.
+ *   - The first call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before starting any stream capture.
+ *   - All calls on one GPU share the one array: two calls that can overlap on
+ *     the GPU (different streams) race on it and give wrong results. */
+#define FF_TOPK_STATIC_MAX_ROWS 4
+int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                          int32_t k, int32_t* status, void* stream);
+
 /* Fused top-k + page-table gather / ragged offset.  Replaces
  * fast_topk_transform_fused and fast_topk_transform_ragged_fused
  * (topk_indexer_radix.cu:1549-1639).
