@@ -39,12 +39,14 @@ namespace cg = cooperative_groups;
 constexpr int kSmemHist = 0;                                   // uint32[kMaxBins]
 constexpr int kSmemStage = kSmemHist + kMaxBins * 4;           // uint64[kSortCap]; merged slice aliases its head
 constexpr int kSmemSort = kSmemStage + kSortCap * 8;           // uint64[kSortCap] survivor list (every CTA)
-constexpr int kSmemCand = kSmemSort + kSortCap * 8;            // uint64[kCandCap]
-constexpr int kSmemRing = kSmemCand + kCandCap * 8;            // ring of score tiles; work lists in the finish
-constexpr int kTileUnits = 2048;                               // 16-byte units per tile (32 KiB)
+constexpr int kSmemRing = kSmemSort + kSortCap * 8;            // ring of score tiles; work lists in the finish
+constexpr int kSmemCand = kSmemRing;                           // uint64[kCandCap]: deeper levels only, after the ring's last use
+// One bulk copy costs about 0.3 us on top of its transfer time and an SM runs
+// them one after the other (measured), so tiles are as large as shared memory allows.
+constexpr int kTileUnits = 4096;                               // 16-byte units per tile (64 KiB)
 constexpr int kTileBytes = kTileUnits * 16;
-static_assert(kTileUnits % kThreads == 0 && kTileUnits / kThreads <= 4, "a thread reads at most 4 units of a tile");
-constexpr int kStages = 3;                                     // tiles in the ring (96 KiB)
+static_assert(kTileUnits % kThreads == 0 && kTileUnits / kThreads <= 8, "a thread reads at most 8 units of a tile");
+constexpr int kStages = 2;                                     // tiles in the ring (128 KiB)
 constexpr int kMinStages = kStages;
 constexpr int kMaxStages = kStages;
 constexpr int kWaitLimit = 1 << 22;                            // bounded mbarrier polling
@@ -381,9 +383,9 @@ __device__ __noinline__ void classify_value(const LevelCtx* c, float x, int32_t 
 }
 
 // Second sweep over one tile: every value not below vmin is a hit; the hits'
-// composites are appended to list[0, cap).  A warp tests its 16 values per lane
+// composites are appended to list[0, cap).  A warp tests its 32 values per lane
 // with float compares and votes once.  Only a warp that saw a hit assigns list
-// slots: the per-lane hit counts (0..16) are prefix-summed with five ballots over
+// slots: the per-lane hit counts (0..32) are prefix-summed with six ballots over
 // their bit planes, one lane does the single shared atomic, and each lane then
 // walks its own hit bits, re-reading the value from the tile.
 __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
@@ -408,9 +410,11 @@ __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first
     const uint32_t b2 = __ballot_sync(0xffffffffu, n & 4u);
     const uint32_t b3 = __ballot_sync(0xffffffffu, n & 8u);
     const uint32_t b4 = __ballot_sync(0xffffffffu, n & 16u);
+    const uint32_t b5 = __ballot_sync(0xffffffffu, n & 32u);
     const int before = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt) + 8 * __popc(b3 & lt) +
-                       16 * __popc(b4 & lt);
-    const int total = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3) + 16 * __popc(b4);
+                       16 * __popc(b4 & lt) + 32 * __popc(b5 & lt);
+    const int total = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3) + 16 * __popc(b4) +
+                      32 * __popc(b5);
     int base = 0;
     if (lane == 0) base = atomicAdd(counter, total);
     base = __shfl_sync(0xffffffffu, base, 0);
@@ -776,35 +780,18 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     // At level 0 "digit >= t" is exactly "value >= value(t << 20)" (unless t lies in
     // the NaN range), so the chunk is swept with float compares only.
     bool swept = false;
-    if (!HAS_MAP && level == 0 && (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
+    if (!HAS_MAP && level == 0 && final_level && (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
       const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
-      uint64_t* list = final_level ? stage : cand;
-      int* counter = final_level ? &sh.stage_count : &sh.cand_count;
-      const int cap = final_level ? kSortCap : kCandCap;
       stream_again(ts, [&](uint32_t tile, int tt, int units) {
-        collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, list, cap, counter);
+        collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, stage, kSortCap, &sh.stage_count);
       });
       float x = 0.f;
       const int pos = partial_element(chunk, x);
       if (pos >= 0 && !(x < vmin)) {
-        const int slot = atomicAdd(counter, 1);
-        if (slot < cap) list[slot] = make_comp(key_of(x), pos);
+        const int slot = atomicAdd(&sh.stage_count, 1);
+        if (slot < kSortCap) stage[slot] = make_comp(key_of(x), pos);
       }
-      if (final_level) {
-        swept = true;
-      } else {
-        // winners and candidates together; they are classified from the buffer
-        __syncthreads();
-        if (sh.cand_count <= kCandCap) {
-          src_is_cand = true;
-          cand_n = sh.cand_count;
-          ctx.compact = false;
-        } else {
-          __syncthreads();
-          if (tid == 0) sh.cand_count = 0;   // too many for the buffer: generic sweep below
-          __syncthreads();
-        }
-      }
+      swept = true;
     }
     if (swept) {
       // nothing left to do for this level
@@ -918,12 +905,12 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   // are spread over all threads, and that work is shared out over the cluster
   // by element.  The loops are deliberately not unrolled: this code runs once
   // per row and its instruction footprint costs more than its trip counts.
-  uint32_t* E = reinterpret_cast<uint32_t*>(smem + kSmemCand);                     // #(bin > b), padded index
+  uint32_t* E = reinterpret_cast<uint32_t*>(smem + kSmemRing);                     // #(bin > b), padded index
   uint64_t* bucketed = stage;
-  uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing);                     // bucket sizes, padded index
-  uint16_t* at_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 20 * 1024);     // slot of survivor i
-  uint32_t* rankcnt = reinterpret_cast<uint32_t*>(smem + kSmemRing + 28 * 1024);    // per slot: #greater in bucket
-  uint32_t* units = reinterpret_cast<uint32_t*>(smem + kSmemRing + 44 * 1024);      // (slot << 8) | chunk, <= 8192
+  uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing + 20 * 1024);                   // bucket sizes, padded index
+  uint16_t* at_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 40 * 1024);     // slot of survivor i
+  uint32_t* rankcnt = reinterpret_cast<uint32_t*>(smem + kSmemRing + 48 * 1024);    // per slot: #greater in bucket
+  uint32_t* units = reinterpret_cast<uint32_t*>(smem + kSmemRing + 64 * 1024);      // (slot << 8) | chunk, <= 8192
   auto pad = [](uint32_t b) { return b + (b >> 3); };   // 8 consecutive bins per thread -> distinct banks
   constexpr int kPadBins = kMaxBins + kMaxBins / 8;
   // bounds of the survivors' composites: exact on the key half, and exact on the
@@ -941,7 +928,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   hmin = __reduce_min_sync(0xffffffffu, hmin);
   lmax = __reduce_max_sync(0xffffffffu, lmax);
   lmin = __reduce_min_sync(0xffffffffu, lmin);
-  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 76 * 1024);   // 4 x kWarps words
+  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 96 * 1024);   // 4 x kWarps words
   if ((tid & 31) == 0) {
     red4[tid >> 5] = hmax;
     red4[kWarps + (tid >> 5)] = hmin;
@@ -1009,7 +996,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   // entries are cut into units of 16 entries; larger ones (many equal keys next
   // to a far outlier) are scanned by a whole warp per element.
   constexpr uint32_t kUnitBucket = 32u;
-  uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 78 * 1024);   // slots, <= kSortCap
+  uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 98 * 1024);   // slots, <= kSortCap
 #pragma unroll 1
   for (int i = tid * n_share + my_share; i < T; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];

@@ -40,8 +40,8 @@ def trace_once(score, lengths, k, cluster=0):
     dev = score.device
     lib.ff_topk_set_cluster_override(cluster)
     C = lib.ff_topk_policy_cluster_size(score.shape[0], score.shape[1], k)
-    n = score.shape[0] * C
-    buf = torch.zeros((n, 32), dtype=torch.int64, device=dev)
+    # a row may be split over up to 64 clusters of up to 16 CTAs: size the buffer for the largest grid
+    buf = torch.zeros((score.shape[0] * 1024, 32), dtype=torch.int64, device=dev)
     out = torch.empty((score.shape[0], k), dtype=torch.int32, device=dev)
     for _ in range(3):
         fast_topk_v3(score, lengths, k, out=out)
@@ -53,7 +53,9 @@ def trace_once(score, lengths, k, cluster=0):
     finally:
         lib.ff_topk_set_trace_buffer(None)
         lib.ff_topk_set_cluster_override(0)
-    return C, buf.cpu().numpy()
+    t = buf.cpu().numpy()
+    used = int((t[:, 0] != 0).sum())          # CTAs that wrote a start stamp
+    return C, t[:max(used, 1)]
 
 
 def format_timeline(stamps, mhz):
