@@ -386,7 +386,7 @@ def bench_cp(args):
     n_rot = 32
     shards = make_rows(n_rot, L_SHARD, dev, seed=1000 + rank)       # this rank's columns of 32 distinct rows
     lengths = torch.tensor([L], dtype=torch.int32, device=dev)
-    plan = ContextParallelTopk(1, k, dev)
+    plan = ContextParallelTopk(1, k, dev, exchange=args.exchange)
     offset = rank * L_SHARD
 
     def step(i):
@@ -396,6 +396,31 @@ def bench_cp(args):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
+    # With the peer-memory exchange a step is three kernel launches and no library call, so the
+    # K steps are captured into one CUDA graph (the step counter lives in device memory);
+    # with the NCCL exchange they are launched eagerly.
+    graph = None
+    side = torch.cuda.Stream()
+    if plan.exchange == "p2p" and not args.no_graph:
+        try:
+            with torch.cuda.stream(side):
+                before_cap = lib.ff_topk_launch_count()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(K):
+                        step(i)
+                launches_per_replay = lib.ff_topk_launch_count() - before_cap
+            graph = g
+        except Exception:
+            graph = None
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)           # all ranks replay a graph, or none does
+    if int(ok.item()) == 0:
+        graph = None
+    if graph is not None:
+        with torch.cuda.stream(side):
+            graph.replay()                                  # untimed: upload + warm-up
+        side.synchronize()
     before = lib.ff_topk_launch_count()
     sampler = ClockSampler(local)
     sampler.start()
@@ -404,14 +429,21 @@ def bench_cp(args):
     dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    e0.record()
-    for i in range(K):
-        step(i)
-    e1.record()
+    if graph is not None:
+        with torch.cuda.stream(side):
+            e0.record(side)
+            graph.replay()
+            e1.record(side)
+        side.synchronize()
+    else:
+        e0.record()
+        for i in range(K):
+            step(i)
+        e1.record()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     dist.barrier()
-    launches = lib.ff_topk_launch_count() - before
+    launches = launches_per_replay if graph is not None else lib.ff_topk_launch_count() - before
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     clocks = sampler.summary(t0, t1)
@@ -457,8 +489,11 @@ def bench_cp(args):
                                    f"{world} contiguous shards of {L_SHARD} columns",
                        "B": 1, "L": L, "k": k, "parallelism": f"cp{world}",
                        "l2": f"each rank rotates over {n_rot} distinct 4 MiB shards (128 MiB > 126 MB L2)",
-                       "timing": "eager stream launches, CUDA events, max over ranks",
-                       "exchange": "NCCL all-gather of (value, global index) candidates, 16 KiB per rank"},
+                       "timing": ("K steps in one CUDA graph replay" if graph is not None else
+                                  "eager stream launches") + ", CUDA events, max over ranks",
+                       "exchange": ("stores into every peer's receive buffer over NVLink + flags (16 KiB per "
+                                    "rank per peer), merge waits on local flags" if plan.exchange == "p2p" else
+                                    "NCCL all-gather of (value, global index) candidates, 16 KiB per rank")},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak * world, "unit": "GB/s",
                          "frac": round(achieved / (peak * world), 5), "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": algo_bytes,
@@ -469,6 +504,7 @@ def bench_cp(args):
             "clocks": clocks,
         }
         print(json.dumps(line))
+    plan.close()
     dist.destroy_process_group()
 
 
@@ -511,6 +547,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: launch the steps eagerly instead of replaying a graph")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "p2p", "nccl"], help="N > 1: candidate exchange")
     ap.add_argument("--profile-case", default=None, choices=["headline", "unique16k", "b64"],
                     help="run a few eager launches of one configuration and exit (for ncu)")
     args = ap.parse_args()

@@ -42,6 +42,23 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int64,
          c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    "ff_cp_exchange_create": (c_int, [c_int32, c_int32, c_int32, c_int32, ctypes.POINTER(c_void_p)]),
+    "ff_cp_exchange_bytes": (c_int64, [c_void_p]),
+    "ff_cp_exchange_base": (c_void_p, [c_void_p]),
+    "ff_cp_exchange_ipc_handle": (c_int, [c_void_p, c_void_p]),
+    "ff_cp_exchange_open_peers": (c_int, [c_void_p, c_void_p, c_int32]),
+    "ff_cp_exchange_set_peer": (c_int, [c_void_p, c_int32, c_void_p]),
+    "ff_cp_exchange_destroy": (c_int, [c_void_p]),
+    "ff_topk_cp_send": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
+    "ff_topk_cp_recv_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ff_topk_cp_step": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p,
+         c_void_p],
+    ),
     "ff_topk_cp_merge": (
         c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int32, c_int32,

@@ -17,7 +17,7 @@ CSRC = Path(__file__).resolve().parent / "csrc"
 INCLUDE = Path(__file__).resolve().parent.parent / "include"
 LIB_NAME = "libff_topk.so"
 SOURCES = ["ff_topk.cu"]
-HEADERS = ["ff_topk_common.cuh", "ff_topk_kernel.cuh"]
+HEADERS = ["ff_topk_common.cuh", "ff_topk_kernel.cuh", "ff_cp_exchange.cuh"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

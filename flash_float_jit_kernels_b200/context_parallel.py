@@ -7,10 +7,17 @@ the unsharded row.
 
 Three steps per call, all on the current stream:
   1. local select on the shard -> ``k`` candidates ``(value, global index)``
-     per row, in canonical order (``ff_topk_cp_local``);
-  2. all-gather of the candidate blocks (NCCL over NVLink; ``2*B*k*4`` bytes
-     per rank);
-  3. exact merge-select of the ``P*k`` candidates (``ff_topk_cp_merge``).
+     per row, in canonical order;
+  2. exchange of the candidate blocks (``2*B*k*4`` bytes per rank);
+  3. exact merge-select of the ``P*k`` candidates.
+
+Two exchanges are implemented.  ``p2p`` (default on GPUs): every rank stores its
+block straight into every peer's receive buffer over NVLink (peer memory mapped
+through CUDA IPC) and raises a flag there; the merge kernel waits on its local
+flags with a bounded wait -- three kernel launches per step, no collective
+library call (``ff_topk_cp_step``).  ``nccl``: ``all_gather_into_tensor`` between
+``ff_topk_cp_local`` and ``ff_topk_cp_merge``; kept as the baseline and as the
+fallback when peer memory cannot be mapped.
 
 Exactness: shards are contiguous, so the order (value desc, global index asc)
 restricted to one shard equals that shard's local order; every global winner
@@ -18,6 +25,7 @@ is among its shard's local top-k; merging under the same total order is exact.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Tuple
 
 import torch
@@ -48,18 +56,74 @@ class ContextParallelTopk:
     nothing.  ``group`` is a ``torch.distributed`` process group (NCCL on GPUs).
     """
 
-    def __init__(self, B: int, topk: int, device: torch.device, group=None):
+    def __init__(self, B: int, topk: int, device: torch.device, group=None, exchange: str = "auto"):
         _require(1 <= topk <= _lib.FF_TOPK_MAX_K, f"topk must be in [1, {_lib.FF_TOPK_MAX_K}]")
+        _require(exchange in ("auto", "p2p", "nccl"), "exchange must be 'auto', 'p2p' or 'nccl'")
         self.B = B
         self.k = topk
         self.device = torch.device(device)
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._ex = None
+        self.exchange = "nccl"
+        if exchange != "nccl" and self.device.type == "cuda":
+            if self._setup_p2p():
+                self.exchange = "p2p"
+            elif exchange == "p2p":
+                raise RuntimeError("peer-memory exchange could not be set up on every rank")
         # plane 0: value bits, plane 1: global index
         self.send = torch.empty((2, B, topk), dtype=torch.int32, device=self.device)
         self.recv = torch.empty((self.world, 2, B, topk), dtype=torch.int32, device=self.device)
         self.out = torch.empty((B, topk), dtype=torch.int32, device=self.device)
+
+    # -- peer-memory exchange ---------------------------------------------
+    def _setup_p2p(self) -> bool:
+        """Allocates this rank's exchange buffers and maps every peer's (CUDA IPC).
+        All ranks agree on the outcome; on any failure everything is released."""
+        lib = _lib.load()
+        handle = ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            ok = lib.ff_cp_exchange_create(self.world, self.rank, self.B, self.k, ctypes.byref(handle)) == 0
+            blob = ctypes.create_string_buffer(64)
+            if ok and self.world > 1:
+                ok = lib.ff_cp_exchange_ipc_handle(handle, blob) == 0
+            if self.world > 1:
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, (ok, blob.raw), group=self.group)
+                ok = all(g[0] for g in gathered)
+                if ok:
+                    handles = b"".join(g[1] for g in gathered)
+                    ok = lib.ff_cp_exchange_open_peers(handle, handles, self.world) == 0
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, ok, group=self.group)
+                ok = all(gathered)
+            if not ok:
+                if handle.value:
+                    lib.ff_cp_exchange_destroy(handle)
+                return False
+        self._ex = handle
+        return True
+
+    def close(self) -> None:
+        """Releases the peer mappings and buffers (collective: every rank calls it)."""
+        if self._ex is not None:
+            torch.cuda.synchronize(self.device)
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            _lib.load().ff_cp_exchange_destroy(self._ex)
+            self._ex = None
+
+    def _step_p2p(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> None:
+        lib = _lib.load()
+        B, L = score_shard.size(0), score_shard.size(1)
+        ws, ws_bytes = _workspace(lib, score_shard.device, B, L, self.k)
+        with torch.cuda.device(score_shard.device):
+            rc = lib.ff_topk_cp_step(
+                self._ex, score_shard.data_ptr(), score_shard.stride(0) if B > 1 else max(score_shard.stride(0), L),
+                lengths.data_ptr(), self.out.data_ptr(), L, shard_offset, _ptr(ws), ws_bytes, None,
+                _stream_ptr(score_shard.device))
+        _lib.check(rc, "ff_topk_cp_step")
 
     # -- step 1 ---------------------------------------------------------
     def _local(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> None:
@@ -100,6 +164,9 @@ class ContextParallelTopk:
         _require(lengths.dim() == 1 and lengths.size(0) == self.B and lengths.dtype == torch.int32
                  and lengths.is_contiguous(), "lengths must be contiguous int32 [B]")
         _require(shard_offset >= 0, "shard_offset must be >= 0")
+        if self._ex is not None:
+            self._step_p2p(score_shard, lengths, int(shard_offset))
+            return self.out
         self._local(score_shard, lengths, int(shard_offset))
         self._exchange()
         self._merge(lengths)

@@ -448,4 +448,160 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
   return launch<true>(p, choose_cluster(device, B, n_cand, k), static_cast<cudaStream_t>(stream));
 }
 
+// ---- context-parallel exchange over peer memory -----------------------------
+
+struct FfCpExchange {
+  int world, rank, B, k, device;
+  size_t slot_words;     // one rank's candidate block: value plane then index plane, 2*B*k words rounded up to 4
+  size_t flag_offset;    // words from the allocation's start to the flags
+  size_t send_offset;    // words from the allocation's start to the send block
+  size_t total_bytes;
+  uint32_t* base;        // this rank's allocation
+  void* peer[ff::kMaxPeers];
+  bool opened[ff::kMaxPeers];
+};
+
+int ff_cp_exchange_create(int32_t world, int32_t rank, int32_t B, int32_t k, void** out) {
+  if (out == nullptr) return fail(FF_ERR_NULL, "out must not be NULL");
+  if (world < 1 || world > ff::kMaxPeers || rank < 0 || rank >= world)
+    return fail(FF_ERR_BAD_SHAPE, "world must be in [1, 16] and rank in [0, world)");
+  if (B < 1 || k < 1 || k > FF_TOPK_MAX_K) return fail(FF_ERR_BAD_K, "B >= 1 and k in [1, 2048] required");
+  int device = 0;
+  int rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  FfCpExchange* ex = new FfCpExchange();
+  ex->world = world;
+  ex->rank = rank;
+  ex->B = B;
+  ex->k = k;
+  ex->device = device;
+  ex->slot_words = (2 * static_cast<size_t>(B) * k + 3) & ~static_cast<size_t>(3);
+  ex->flag_offset = 2 * static_cast<size_t>(world) * ex->slot_words;
+  ex->send_offset = ex->flag_offset + 64;   // 2 * kMaxPeers flags + the step counter, padded to 256 bytes
+  ex->total_bytes = (ex->send_offset + ex->slot_words) * sizeof(uint32_t);
+  for (int i = 0; i < ff::kMaxPeers; ++i) {
+    ex->peer[i] = nullptr;
+    ex->opened[i] = false;
+  }
+  cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ex->base), ex->total_bytes);
+  if (e == cudaSuccess) e = cudaMemset(ex->base, 0, ex->total_bytes);
+  if (e != cudaSuccess) {
+    delete ex;
+    return fail_cuda(e, "ff_cp_exchange_create");
+  }
+  ex->peer[rank] = ex->base;
+  *out = ex;
+  return 0;
+}
+
+int64_t ff_cp_exchange_bytes(void* handle) {
+  return handle == nullptr ? 0 : static_cast<int64_t>(static_cast<FfCpExchange*>(handle)->total_bytes);
+}
+
+void* ff_cp_exchange_base(void* handle) {
+  return handle == nullptr ? nullptr : static_cast<FfCpExchange*>(handle)->base;
+}
+
+int ff_cp_exchange_ipc_handle(void* handle, void* out64) {
+  if (handle == nullptr || out64 == nullptr) return fail(FF_ERR_NULL, "NULL argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, static_cast<FfCpExchange*>(handle)->base);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaIpcGetMemHandle");
+  memcpy(out64, &h, 64);
+  return 0;
+}
+
+int ff_cp_exchange_open_peers(void* handle, const void* handles, int32_t n) {
+  if (handle == nullptr || handles == nullptr) return fail(FF_ERR_NULL, "NULL argument");
+  FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  if (n != ex->world) return fail(FF_ERR_BAD_SHAPE, "one handle per rank expected");
+  for (int p = 0; p < ex->world; ++p) {
+    if (p == ex->rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, static_cast<const char*>(handles) + 64 * p, 64);
+    void* ptr = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaIpcOpenMemHandle");
+    ex->peer[p] = ptr;
+    ex->opened[p] = true;
+  }
+  return 0;
+}
+
+int ff_cp_exchange_set_peer(void* handle, int32_t p, void* peer_base) {
+  if (handle == nullptr || peer_base == nullptr) return fail(FF_ERR_NULL, "NULL argument");
+  FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  if (p < 0 || p >= ex->world) return fail(FF_ERR_BAD_SHAPE, "peer out of range");
+  ex->peer[p] = peer_base;
+  return 0;
+}
+
+int ff_cp_exchange_destroy(void* handle) {
+  if (handle == nullptr) return 0;
+  FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  for (int p = 0; p < ex->world; ++p) {
+    if (ex->opened[p]) (void)cudaIpcCloseMemHandle(ex->peer[p]);
+  }
+  (void)cudaFree(ex->base);
+  delete ex;
+  return 0;
+}
+
+int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                    int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream) {
+  if (handle == nullptr) return fail(FF_ERR_NULL, "exchange handle must not be NULL");
+  FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  for (int p = 0; p < ex->world; ++p)
+    if (ex->peer[p] == nullptr) return fail(FF_ERR_NULL, "exchange: a peer is not mapped yet");
+  uint32_t* send = ex->base + ex->send_offset;
+  const size_t plane = static_cast<size_t>(ex->B) * ex->k;
+  int rc = ff_topk_cp_local(scores, row_stride, lengths, reinterpret_cast<int32_t*>(send + plane),
+                            reinterpret_cast<float*>(send), ex->B, L_width, ex->k, shard_offset, workspace,
+                            workspace_bytes, status, stream);
+  if (rc != 0) return rc;
+  ff::PeerPtrs peers;
+  for (int p = 0; p < ff::kMaxPeers; ++p) peers.base[p] = static_cast<uint32_t*>(p < ex->world ? ex->peer[p] : nullptr);
+  ff::cp_push_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      send, peers, ex->world, ex->rank, static_cast<int>(2 * plane), ex->slot_words, ex->flag_offset);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "cp_push_kernel");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx, int32_t* status,
+                          void* stream) {
+  if (handle == nullptr || lengths == nullptr || out_idx == nullptr) return fail(FF_ERR_NULL, "NULL argument");
+  FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  ff::CpMergeParams p = {};
+  p.recv_even = ex->base;
+  p.parity_stride = static_cast<int64_t>(ex->world) * static_cast<int64_t>(ex->slot_words);
+  p.slot_words = static_cast<int64_t>(ex->slot_words);
+  p.flags = ex->base + ex->flag_offset;
+  p.lengths = lengths;
+  p.out_idx = out_idx;
+  p.status = status;
+  p.world = ex->world;
+  p.B = ex->B;
+  p.k = ex->k;
+  const int n_cand = ex->world * ex->k;
+  const dim3 grid((n_cand + 1023) / 1024, ex->B, 1);
+  ff::cp_merge_sorted_kernel<<<grid, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "cp_merge_sorted_kernel");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                    int32_t* out_idx, int64_t L_width, int64_t shard_offset, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream) {
+  const int rc = ff_topk_cp_send(handle, scores, row_stride, lengths, L_width, shard_offset, workspace,
+                                 workspace_bytes, status, stream);
+  if (rc != 0) return rc;
+  return ff_topk_cp_recv_merge(handle, lengths, out_idx, status, stream);
+}
+
 }  // extern "C"

@@ -76,6 +76,9 @@ struct TopkParams {
   int32_t* status;             // optional soft-error word
   int32_t groups;              // clusters per row (> 1 needs workspace and a cooperative launch)
   uint32_t* workspace;         // zero-filled global scratch, kWsRowWords words per row
+  const uint32_t* wait_flags;  // merge mode: [2][16] flags raised by the peers' pushes, step counter after them; or null
+  int32_t wait_n;              // number of peers
+  int64_t parity_stride;       // elements between the receive buffers of even and odd steps
   unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
 

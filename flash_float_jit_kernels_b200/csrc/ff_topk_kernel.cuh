@@ -29,6 +29,7 @@
 
 #include <cooperative_groups.h>
 
+#include "ff_cp_exchange.cuh"
 #include "ff_topk_common.cuh"
 
 namespace ff {
@@ -626,6 +627,17 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   const int tid = threadIdx.x;
   const int k = p.k;
 
+  // ---- context-parallel merge: the candidates are only valid once every peer has pushed ----
+  int64_t recv_shift = 0;   // elements from the even-step receive buffer to the one of this step
+  if (HAS_MAP && p.wait_flags != nullptr) {
+    const uint32_t step = p.wait_flags[kEpochWord];   // written by this step's push kernel (earlier launch)
+    const int parity = static_cast<int>(step & 1u);
+    recv_shift = parity * p.parity_stride;
+    if (!wait_for_peers(p.wait_flags + parity * kMaxPeers, p.wait_n, step) && p.status != nullptr &&
+        threadIdx.x == 0)
+      atomicOr(p.status, 2);
+  }
+
   // ---- row geometry (uniform over the cluster) ---------------------------
   const int rs = p.row_starts != nullptr ? p.row_starts[row] : 0;
   const int glen = p.lengths != nullptr ? p.lengths[row] : 0;
@@ -639,9 +651,9 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     if (l < 0) l = 0;
     len = static_cast<int>(l);
   }
-  const float* rowp = p.scores + static_cast<int64_t>(row) * p.row_stride + rs;
+  const float* rowp = p.scores + static_cast<int64_t>(row) * p.row_stride + rs + recv_shift;
   const int32_t* imap =
-      HAS_MAP ? p.idx_map + static_cast<int64_t>(row) * p.row_stride + rs : nullptr;
+      HAS_MAP ? p.idx_map + static_cast<int64_t>(row) * p.row_stride + rs + recv_shift : nullptr;
 
   int table_row = row;
   if (p.epilogue == 1 && p.cu_seqlens_q != nullptr) {
@@ -658,6 +670,23 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
   if (identity || len <= k) {
     if (my_share != 0) return;
+    if (!HAS_MAP && p.out_val != nullptr) {
+      // Context-parallel shard shorter than k: every position is a candidate, but the
+      // merge expects the run in canonical order, so rank the few elements by counting.
+      for (int j = tid; j < len; j += kThreads) stage[j] = make_comp(key_of(rowp[j]), j);
+      __syncthreads();
+      for (int j = tid; j < k; j += kThreads) {
+        if (j >= len) {
+          emit(p, row, j, -1, 0u, false, table_row);
+          continue;
+        }
+        const uint64_t c = stage[j];
+        int pos = 0;
+        for (int q = 0; q < len; ++q) pos += stage[q] > c ? 1 : 0;
+        emit(p, row, pos, comp_index(c), comp_key(c), false, table_row);
+      }
+      return;
+    }
     for (int j = tid; j < k; j += kThreads) {
       if (HAS_MAP && !identity) {
         // no more candidates than k slots: pass them through in position order

@@ -146,6 +146,38 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
                      int32_t k, void* workspace, size_t workspace_bytes, int32_t* status,
                      void* stream);
 
+/* ---- Context-parallel mode with the exchange fused over peer memory --------
+ * (No reference counterpart.)  Instead of a collective library call, each rank
+ * stores its candidates straight into every peer's receive buffer over NVLink
+ * and raises a flag there; the merge kernel polls its own flags (bounded to one
+ * second, FF_STATUS_WAIT_TIMEOUT on expiry) and reads local memory only.
+ *
+ *   ff_cp_exchange_create      allocates this rank's buffers (cudaMalloc) for a fixed (world, B, k)
+ *   ff_cp_exchange_ipc_handle  64-byte cudaIpcMemHandle_t of that allocation, to be sent to the peers
+ *   ff_cp_exchange_open_peers  maps the peers' allocations from `n` = world handles (rank-major, 64 B each)
+ *   ff_cp_exchange_set_peer    in-process alternative: give peer p's base pointer directly
+ *   ff_topk_cp_send            shard-local select + push to all peers (2 launches)
+ *   ff_topk_cp_recv_merge      wait for all peers' pushes of the current step + merge (1 launch)
+ *   ff_topk_cp_step            send followed by recv_merge
+ * Every rank must call the step functions the same number of times in the same
+ * order; a rank may run at most one step ahead of its peers (two alternating
+ * receive buffers).  out_idx is [B, k] global indices, identical on all ranks. */
+int ff_cp_exchange_create(int32_t world, int32_t rank, int32_t B, int32_t k, void** handle_out);
+int64_t ff_cp_exchange_bytes(void* handle);
+void* ff_cp_exchange_base(void* handle);
+int ff_cp_exchange_ipc_handle(void* handle, void* out64);
+int ff_cp_exchange_open_peers(void* handle, const void* handles, int32_t n);
+int ff_cp_exchange_set_peer(void* handle, int32_t peer, void* peer_base);
+int ff_cp_exchange_destroy(void* handle);
+int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                    int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream);
+int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx, int32_t* status,
+                          void* stream);
+int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                    int32_t* out_idx, int64_t L_width, int64_t shard_offset, void* workspace,
+                    size_t workspace_bytes, int32_t* status, void* stream);
+
 /* Test / tuning hook: force the thread-block-cluster size per row
  * (0 = automatic policy, else 1, 2, 4, 8 or 16).  Process-wide. */
 int ff_topk_set_cluster_override(int32_t cluster_size);

@@ -176,6 +176,12 @@ def cp_local(score_shard: np.ndarray, lengths: np.ndarray, k: int, shard_offset:
     B, Lw = score_shard.shape
     loc = np.clip(lengths.astype(np.int64) - shard_offset, 0, Lw).astype(np.int32)
     idx = topk_numpy(score_shard, loc, k)
+    for b in range(B):          # a shard shorter than k still emits its run in canonical order
+        n = int(loc[b])
+        if 0 < n <= k:
+            key = monotone_key(score_shard[b, :n]).astype(np.uint64)
+            comp = (key << np.uint64(32)) | (~np.arange(n, dtype=np.uint32)).astype(np.uint64)
+            idx[b, :n] = np.argsort(comp)[::-1].astype(np.int32)
     val = np.full((B, k), -np.inf, dtype=np.float32)
     gidx = np.full((B, k), -1, dtype=np.int32)
     for b in range(B):

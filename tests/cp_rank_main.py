@@ -56,13 +56,16 @@ def main():
         a, b = shard_bounds(L, world, rank)
         shard = s[:, a:b].contiguous().to(device)
         plan_cls = ContextParallelTopk if backend == "nccl" else OracleStepsPlan
-        plan = plan_cls(B, k, device)
-        for _ in range(2):                                   # buffers are reused across calls
-            out = plan(shard, lengths.to(device), a)
-        if device.type == "cuda":
-            torch.cuda.synchronize()
         exp = oracle.topk_c(s.numpy(), lengths.numpy(), k)
-        assert np.array_equal(out.cpu().numpy(), exp), f"rank {rank}: mismatch B={B} L={L} k={k}"
+        for exchange in (("p2p", "nccl") if backend == "nccl" else ("nccl",)):
+            plan = plan_cls(B, k, device, exchange=exchange)
+            assert plan.exchange == exchange
+            for _ in range(3):                               # buffers are reused across calls
+                out = plan(shard, lengths.to(device), a)
+            if device.type == "cuda":
+                torch.cuda.synchronize()
+            assert np.array_equal(out.cpu().numpy(), exp), f"rank {rank}: mismatch B={B} L={L} k={k} {exchange}"
+            plan.close()
         # every rank holds the same answer
         gathered = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(gathered, out)

@@ -80,3 +80,110 @@ def test_real_ranks_over_nccl():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=str(ROOT))
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "CP_OK" in res.stdout
+
+
+# ---- peer-memory exchange (ff_topk_cp_send / ff_topk_cp_recv_merge) -------------------------
+def _make_exchanges(lib, P, B, k):
+    import ctypes
+    exs = []
+    for r in range(P):
+        h = ctypes.c_void_p()
+        assert lib.ff_cp_exchange_create(P, r, B, k, ctypes.byref(h)) == 0, lib.ff_last_error_string()
+        exs.append(h)
+    for r in range(P):                       # same process: hand the peers' base pointers over directly
+        for p in range(P):
+            assert lib.ff_cp_exchange_set_peer(exs[r], p, lib.ff_cp_exchange_base(exs[p])) == 0
+    return exs
+
+
+@pytest.mark.parametrize("P", [1, 2, 4, 8])
+def test_peer_exchange_emulated_on_one_device(oracle, P):
+    """All P ranks live on one GPU.  Every rank's send is enqueued before any merge, so no
+    kernel ever waits for a later launch; three steps exercise both receive buffers."""
+    from flash_float_jit_kernels_b200 import _lib, shard_bounds
+    lib = _lib.load()
+    lib.ff_topk_set_cluster_override(0)
+    dev = torch.device("cuda:0")
+    B, L, k = 2, 600000, 1024
+    exs = _make_exchanges(lib, P, B, k)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        for step in range(3):
+            s = torch.randn((B, L), generator=torch.Generator().manual_seed(300 + step)).to(torch.bfloat16).float()
+            lengths = torch.tensor([L, L - 999 * step - 1], dtype=torch.int32)
+            sd, ld = s.to(dev), lengths.to(dev)
+            for r in range(P):
+                a, b = shard_bounds(L, P, r)
+                shard = sd[:, a:b]
+                assert lib.ff_topk_cp_send(exs[r], shard.data_ptr(), shard.stride(0), ld.data_ptr(), b - a, a,
+                                           None, 0, status.data_ptr(), stream) == 0
+            outs = torch.empty((P, B, k), dtype=torch.int32, device=dev)
+            for r in range(P):
+                assert lib.ff_topk_cp_recv_merge(exs[r], ld.data_ptr(), outs[r].data_ptr(), status.data_ptr(),
+                                                 stream) == 0
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
+            exp = oracle.topk_c(s.numpy(), lengths.numpy(), k)
+            for r in range(P):
+                assert np.array_equal(outs[r].cpu().numpy(), exp), f"step {step} rank {r}"
+    finally:
+        torch.cuda.synchronize()
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
+
+
+def test_missing_peer_ends_in_a_timeout_status_not_a_hang():
+    """Rank 1 never pushes: rank 0's merge gives up after its one-second bounded wait, reports
+    FF_STATUS_WAIT_TIMEOUT in the status word, and the context stays usable."""
+    from flash_float_jit_kernels_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    B, L, k = 1, 50000, 256
+    exs = _make_exchanges(lib, 2, B, k)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        s = torch.randn((B, L), device=dev)
+        lengths = torch.tensor([2 * L], dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        out = torch.empty((B, k), dtype=torch.int32, device=dev)
+        assert lib.ff_topk_cp_send(exs[0], s.data_ptr(), s.stride(0), lengths.data_ptr(), L, 0, None, 0,
+                                   status.data_ptr(), stream) == 0
+        assert lib.ff_topk_cp_recv_merge(exs[0], lengths.data_ptr(), out.data_ptr(), status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) & 2, "the wait for the absent peer should have timed out"
+        assert float(torch.ones(4, device=dev).sum()) == 4.0           # context still usable
+    finally:
+        torch.cuda.synchronize()
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
+
+
+def test_peer_exchange_with_shards_shorter_than_k(oracle):
+    """Ragged rows: some shards hold fewer than k valid columns (or none); their runs must still
+    arrive in canonical order for the sorted-run merge."""
+    from flash_float_jit_kernels_b200 import _lib, shard_bounds
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    P, B, L, k = 4, 3, 40000, 512
+    exs = _make_exchanges(lib, P, B, k)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        s = torch.randn((B, L), generator=torch.Generator().manual_seed(9)).to(torch.bfloat16).float()
+        lengths = torch.tensor([10100, 300, 39999], dtype=torch.int32)   # row 0 ends 100 columns into shard 1
+        sd, ld = s.to(dev), lengths.to(dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        for r in range(P):
+            a, b = shard_bounds(L, P, r)
+            shard = sd[:, a:b]
+            assert lib.ff_topk_cp_send(exs[r], shard.data_ptr(), shard.stride(0), ld.data_ptr(), b - a, a,
+                                       None, 0, status.data_ptr(), stream) == 0
+        out = torch.empty((B, k), dtype=torch.int32, device=dev)
+        assert lib.ff_topk_cp_recv_merge(exs[2], ld.data_ptr(), out.data_ptr(), status.data_ptr(), stream) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k))
+    finally:
+        torch.cuda.synchronize()
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
