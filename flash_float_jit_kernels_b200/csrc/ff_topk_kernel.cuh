@@ -217,13 +217,22 @@ struct TileStream {
   int n_units;         // fe - fb
   int n_tiles;
   bool timed_out;
+  // ring bookkeeping, mirrored by every thread (only thread 0 issues copies)
+  // (two stages, kept in scalars so that nothing is indexed dynamically)
+  int held0, held1;        // tile in each stage, -1 when empty
+  int fills0, fills1;      // copies issued into the stage so far
+  int fidx0, fidx1;        // index of the copy that brought the held tile (its "full" phase)
+  bool arrived0, arrived1; // the held tile's copy has been waited for
+  int cons0, cons1;        // "all warps are done with the stage" completions so far
+  int passes;              // sweeps done; odd sweeps run in reverse to start on the resident tiles
 };
+static_assert(kStages == 2, "the ring bookkeeping is written for two stages");
 
 __device__ __forceinline__ int tile_units(const TileStream& s, int t) {
   return min(kTileUnits, s.n_units - t * kTileUnits);
 }
 __device__ __forceinline__ void issue_tile(const TileStream& s, int t) {
-  const int stage = t % kStages;
+  const int stage = t & 1;
   const uint32_t bytes = static_cast<uint32_t>(tile_units(s, t)) * 16u;
   const uint32_t bar = s.bars + 8u * stage;
   mbar_expect_tx(bar, bytes);
@@ -235,67 +244,71 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// The ring is refilled without any CTA-wide barrier: every warp arrives on the
-// stage's "empty" mbarrier when it has read its part of the tile, and thread 0
-// refills the stage that was consumed kRefillLag tiles ago, so it rarely has to
-// wait for a slower warp while stages - kRefillLag tiles stay in flight.
-constexpr int kRefillLag = 1;
-
-// First sweep: tiles 0..n-1 in order.  process(tile, t, units) is called by
-// every thread once per tile with the tile's shared-memory address.
-template <typename F>
-__device__ __forceinline__ void stream_forward(TileStream& s, F&& process) {
-  const bool refill = s.n_tiles > kStages;
-  if (threadIdx.x == 0) {
-    const int first = min(s.n_tiles, kStages);
-    for (int t = 0; t < first; ++t) issue_tile(s, t);
-  }
-#pragma unroll 1
-  for (int t = 0; t < s.n_tiles; ++t) {
-    const int stage = t % kStages;
-    if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / kStages) & 1))) s.timed_out = true;
-    process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
-    if (refill) {
-      __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(s.ebars + 8u * stage);
-      const int tr = t - kRefillLag + kStages;
-      if (threadIdx.x == 0 && t >= kRefillLag && tr < s.n_tiles) {
-        // fill number q of a stage waits for the (q-1)-th "all warps done" of that stage
-        const int q = tr / kStages;
-        if (!mbar_wait(s.ebars + 8u * (tr % kStages), static_cast<uint32_t>((q - 1) & 1))) s.timed_out = true;
-        issue_tile(s, tr);
-      }
-    }
-  }
+__device__ __forceinline__ void stream_init(TileStream& s) {
+  s.held0 = s.held1 = -1;
+  s.fills0 = s.fills1 = 0;
+  s.fidx0 = s.fidx1 = 0;
+  s.arrived0 = s.arrived1 = false;
+  s.cons0 = s.cons1 = 0;
+  s.passes = 0;
+  s.timed_out = false;
 }
 
-// Second sweep.  A chunk of at most `stages` tiles is still resident and is read
-// again with no copies at all.  Otherwise the ring holds the LAST `stages` tiles,
-// so the tiles are visited in reverse, each stage being refilled with the tile
-// `stages` below the one just consumed.  Phase bookkeeping: during the first
-// sweep stage s completed its "empty" barrier once per tile it held; here the
-// refill that brings in the tile with q = t / stages waits for the completion of
-// index 2 * fills(s) - 2 - q, whose parity is q & 1, and the tile's "full"
-// barrier completes with parity q & 1 as on its first visit.
+// Puts tile t into its stage (t & 1); every thread records it, thread 0 issues the copy.
+__device__ __forceinline__ void stream_fetch(TileStream& s, int t) {
+  if (t & 1) {
+    s.held1 = t;
+    s.fidx1 = s.fills1++;
+    s.arrived1 = false;
+  } else {
+    s.held0 = t;
+    s.fidx0 = s.fills0++;
+    s.arrived0 = false;
+  }
+  if (threadIdx.x == 0) issue_tile(s, t);
+}
+
+// One sweep over the chunk's tiles; process(tile, t, units) is called by every
+// thread once per tile with the tile's shared-memory address.  Sweeps alternate
+// direction so that each one starts on the tiles the previous one left in the
+// ring; a chunk of at most kStages tiles is copied once and stays resident for
+// all later sweeps.  While a tile is processed the next one is in flight: a stage
+// is refilled, without any CTA-wide barrier, as soon as every warp has arrived
+// on its "empty" mbarrier (one bulk copy at a time is all an SM sustains).
 template <typename F>
-__device__ __forceinline__ void stream_again(TileStream& s, F&& process) {
-  const bool refill = s.n_tiles > kStages;
+__device__ __forceinline__ void stream_pass(TileStream& s, F&& process) {
+  const int n = s.n_tiles;
+  const bool refill = n > kStages;
+  const bool reverse = (s.passes & 1) != 0;
+  s.passes += 1;
+  if (refill || s.held0 < 0) __syncthreads();   // every thread has left the previous sweep before a stage is overwritten
+  for (int i = 0; i < min(n, kStages); ++i) {
+    const int t = reverse ? n - 1 - i : i;
+    if (((t & 1) ? s.held1 : s.held0) != t) stream_fetch(s, t);
+  }
 #pragma unroll 1
-  for (int t = s.n_tiles - 1; t >= 0; --t) {
-    const int stage = t % kStages;
-    if (t < s.n_tiles - kStages) {
-      if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>((t / kStages) & 1))) s.timed_out = true;
+  for (int i = 0; i < n; ++i) {
+    const int t = reverse ? n - 1 - i : i;
+    const int stage = t & 1;
+    if (refill && i >= 1 && i + 1 < n) {
+      // the stage used one step ago gets the tile of the next step
+      const int prev = stage ^ 1;
+      if (threadIdx.x == 0) {
+        const int done = (prev ? s.cons1 : s.cons0) - 1;
+        if (!mbar_wait(s.ebars + 8u * prev, static_cast<uint32_t>(done & 1))) s.timed_out = true;
+      }
+      stream_fetch(s, reverse ? t - 1 : t + 1);
+    }
+    if (!(stage ? s.arrived1 : s.arrived0)) {
+      const int fidx = stage ? s.fidx1 : s.fidx0;
+      if (!mbar_wait(s.bars + 8u * stage, static_cast<uint32_t>(fidx & 1))) s.timed_out = true;
+      if (stage) s.arrived1 = true; else s.arrived0 = true;
     }
     process(s.ring + static_cast<uint32_t>(stage) * kTileBytes, t, tile_units(s, t));
     if (refill) {
       __syncwarp();
       if ((threadIdx.x & 31) == 0) mbar_arrive(s.ebars + 8u * stage);
-      const int tr = t + kRefillLag - kStages;
-      if (threadIdx.x == 0 && t + kRefillLag <= s.n_tiles - 1 && tr >= 0) {
-        if (!mbar_wait(s.ebars + 8u * (tr % kStages), static_cast<uint32_t>((tr / kStages) & 1)))
-          s.timed_out = true;
-        issue_tile(s, tr);
-      }
+      if (stage) s.cons1 += 1; else s.cons0 += 1;
     }
   }
 }
@@ -429,6 +442,33 @@ __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first
       if (pos < cap) list[pos] = make_comp(key_of(x), 4 * (first_unit + lu) - mis + (e & 3));
       ++pos;
     }
+  }
+}
+
+// Like collect_tile, but every value not below vmin is handed to on_hit(x, position)
+// instead of being stored: used by the sweeps of the second digit level, where a
+// hit is either counted in the next histogram or stored after an exact test.
+template <typename F>
+__device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
+                                          F&& on_hit) {
+  uint32_t hits = 0u;
+#pragma unroll
+  for (int j = 0; j < kTileUnits / kThreads; ++j) {
+    const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
+    if (lu < units) {
+      const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
+      const uint32_t h = (!(v.x < vmin) ? 1u : 0u) | (!(v.y < vmin) ? 2u : 0u) |
+                         (!(v.z < vmin) ? 4u : 0u) | (!(v.w < vmin) ? 8u : 0u);
+      hits |= h << (4 * j);
+    }
+  }
+  while (hits != 0u) {
+    const int e = __ffs(hits) - 1;
+    hits &= hits - 1u;
+    const int lu = static_cast<int>(threadIdx.x) + (e >> 2) * kThreads;
+    float x;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 4u * (e & 3)));
+    on_hit(x, 4 * (first_unit + lu) - mis + (e & 3));
   }
 }
 
@@ -716,7 +756,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   ts.ebars = smem_addr(&sh.ebars[0]);
   ts.n_units = chunk.fe - chunk.fb;
   ts.n_tiles = (ts.n_units + kTileUnits - 1) / kTileUnits;
-  ts.timed_out = false;
+  stream_init(ts);
   if (tid == 0) {
     sh.stage_count = 0;
     sh.sort_count = 0;
@@ -736,7 +776,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
         chunk, [](float) { return true; },
         [&](float x, int32_t idx) { atomicAdd(&hist[(idx < 0 ? 0u : key_of(x)) >> 20], 1u); });
   } else {
-    stream_forward(ts, [&](uint32_t tile, int, int units) {
+    stream_pass(ts, [&](uint32_t tile, int, int units) {
 #pragma unroll
       for (int j = 0; j < kTileUnits / kThreads; ++j) {
         const int lu = tid + j * kThreads;
@@ -811,7 +851,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     bool swept = false;
     if (!HAS_MAP && level == 0 && final_level && (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
       const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
-      stream_again(ts, [&](uint32_t tile, int tt, int units) {
+      stream_pass(ts, [&](uint32_t tile, int tt, int units) {
         collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, stage, kSortCap, &sh.stage_count);
       });
       float x = 0.f;
@@ -820,6 +860,48 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
         const int slot = atomicAdd(&sh.stage_count, 1);
         if (slot < kSortCap) stage[slot] = make_comp(key_of(x), pos);
       }
+      swept = true;
+    } else if (!HAS_MAP && !src_is_cand && level == 0 && !final_level &&
+               (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
+      // Too many elements at or above the threshold bin for the finish: winners
+      // (bin > t) go to the stage buffer, the bin's own elements are only counted
+      // in the histogram of the next 10 key bits; the chunk is swept once more
+      // when that digit's threshold is known.
+      const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
+      auto on_hit = [&](float x, int pos) {
+        const uint32_t key = key_of(x);
+        if ((key >> 20) > static_cast<uint32_t>(t)) {
+          push_aggregated(stage, &sh.stage_count, kSortCap, make_comp(key, pos));
+        } else {
+          atomicAdd(&hist[(key >> 10) & 1023u], 1u);
+        }
+      };
+      stream_pass(ts, [&](uint32_t tile, int tt, int units) {
+        scan_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
+      });
+      float x = 0.f;
+      const int pos = partial_element(chunk, x);
+      if (pos >= 0 && !(x < vmin)) on_hit(x, pos);
+      ctx.compact = false;
+      swept = true;
+    } else if (!HAS_MAP && !src_is_cand && level == 1 && final_level) {
+      // Second digit resolved: survivors are the elements of bin P whose next 10
+      // bits are >= t, i.e. 22-bit key prefix in [Pn, Pmax]; float pre-filter on the
+      // lower bound, exact test on the key.
+      const uint32_t key_lo = static_cast<uint32_t>(Pn) << 10;
+      const float vmin = prefilter_value(key_lo);
+      auto on_hit = [&](float x, int pos) {
+        const uint32_t key = key_of(x);
+        const uint32_t pre = key >> 10;
+        if (pre >= static_cast<uint32_t>(Pn) && pre <= static_cast<uint32_t>(Pmax))
+          push_aggregated(stage, &sh.stage_count, kSortCap, make_comp(key, pos));
+      };
+      stream_pass(ts, [&](uint32_t tile, int tt, int units) {
+        scan_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
+      });
+      float x = 0.f;
+      const int pos = partial_element(chunk, x);
+      if (pos >= 0 && !(x < vmin)) on_hit(x, pos);
       swept = true;
     }
     if (swept) {
