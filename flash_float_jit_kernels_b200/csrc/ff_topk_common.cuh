@@ -13,16 +13,19 @@ constexpr int kWarps = kThreads / 32;
 constexpr int kMaxK = 2048;            // largest supported k
 constexpr int kSortCap = 4096;         // survivors the finishing sort can take
 constexpr int kCandCap = 4096;         // per-CTA compacted threshold-bin candidates
-constexpr int kMaxBins = 4096;         // first-level digit: top 12 key bits
+constexpr int kMaxBins = 8192;         // first-level digit: top 13 key bits
+constexpr int kFirstBits = 13;
+constexpr int kFirstShift = 32 - kFirstBits;   // key >> kFirstShift is the first digit
+constexpr int kFinishBins = 4096;      // bins of the finishing counting sort
 constexpr int kMaxCluster = 16;
-constexpr int kNumLevels = 6;          // 12+10+10 key bits, 11+11+10 index bits
+constexpr int kNumLevels = 6;          // 13+10+9 key bits, 11+11+10 index bits
 
 // Digit layout over the 64-bit composite (key << 32 | ~index).
 __host__ __device__ constexpr int level_shift(int l) {
-  return l == 0 ? 52 : l == 1 ? 42 : l == 2 ? 32 : l == 3 ? 21 : l == 4 ? 10 : 0;
+  return l == 0 ? 51 : l == 1 ? 41 : l == 2 ? 32 : l == 3 ? 21 : l == 4 ? 10 : 0;
 }
 __host__ __device__ constexpr int level_bits(int l) {
-  return l == 0 ? 12 : l == 1 ? 10 : l == 2 ? 10 : l == 3 ? 11 : l == 4 ? 11 : 10;
+  return l == 0 ? 13 : l == 1 ? 10 : l == 2 ? 9 : l == 3 ? 11 : l == 4 ? 11 : 10;
 }
 
 // Order-preserving fp32 -> uint32 map: a > b  <=>  key(a) > key(b), with

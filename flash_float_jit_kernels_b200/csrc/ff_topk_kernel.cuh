@@ -5,7 +5,7 @@
 // (jit_kernel/csrc/topk_indexer/topk_indexer_radix.cu:554-997) and the
 // single-CTA topk_kernel_small_k (jit_kernel/csrc/topk_indexer/top_small_k.cuh:84-348).
 // Differences by design: keys are the full order-preserving 32-bit map (any
-// fp32 input, not only [0,256)); the first digit is 12 bits; the CTA's chunk is
+// fp32 input, not only [0,256)); the first digit is 13 bits; the CTA's chunk is
 // streamed through a ring of shared-memory tiles by bulk asynchronous copies and
 // stays resident for the second sweep when it fits; per-CTA histograms are
 // merged as a reduce-scatter over distributed shared memory followed by a
@@ -15,7 +15,7 @@
 // select into the index bits; the output is in canonical order.
 //
 // Stages per row (S = cluster barrier; plain CTA barriers when the cluster is 1 CTA):
-//   sweep 1   12-bit histogram of the CTA's chunk, tiles arriving by cp.async.bulk
+//   sweep 1   13-bit histogram of the CTA's chunk, tiles arriving by cp.async.bulk
 //   S  merge  each CTA sums its slice of bins from every peer's histogram (DSMEM loads)
 //      scan   suffix scan of the slice; slice totals to every peer (DSMEM stores)
 //   S  find   the CTA whose slice holds the crossing publishes (digit, above, count)
@@ -319,12 +319,12 @@ __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
   return v;
 }
 
-// Raw 12-bit digit of a score: sign | exponent | top 3 mantissa bits of x + 0.0f.
+// Raw 13-bit digit of a score: sign | exponent | top 4 mantissa bits of x + 0.0f.
 // The add maps -0.0 to +0.0 and every NaN to the canonical 0x7fffffff, so the
 // digit needs no further special cases; raw_of_bin() translates between this
 // sign-magnitude order and the monotone bin order when the histogram is read.
-__device__ __forceinline__ uint32_t raw_digit(float x) { return __float_as_uint(__fadd_rn(x, 0.0f)) >> 20; }
-__device__ __forceinline__ int raw_of_bin(int m) { return m ^ ((m & 0x800) ? 0x800 : 0xfff); }
+__device__ __forceinline__ uint32_t raw_digit(float x) { return __float_as_uint(__fadd_rn(x, 0.0f)) >> kFirstShift; }
+__device__ __forceinline__ int raw_of_bin(int m) { return m ^ ((m & (kMaxBins >> 1)) ? (kMaxBins >> 1) : (kMaxBins - 1)); }
 
 // Key and composite of one element; ignored merge entries (index < 0) map to 0.
 template <bool HAS_MAP>
@@ -478,8 +478,8 @@ __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_un
 //   [0, 6)   arrivals at the histogram barrier of digit level 0..5
 //   [6]      arrivals at the survivor barrier      [7] CTAs that are done
 //   [8]      survivors appended so far
-//   [64, 64 + 6 * 4096)          one 4096-bin global histogram per digit level
-//   [64 + 6 * 4096, + 2 * 4096)  survivor list (4096 x 64-bit composites)
+//   [64, 64 + 6 * 8192)          one 8192-bin global histogram per digit level
+//   [64 + 6 * 8192, + 2 * 4096)  survivor list (4096 x 64-bit composites)
 constexpr int kWsHeaderWords = 64;
 constexpr int kWsHistWords = kNumLevels * kMaxBins;
 constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kSortCap;
@@ -520,32 +520,62 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   const int tid = threadIdx.x;
   int slice_n = nbins / C;
   int slice_base = rank * slice_n;
-  if (C > 1) {
+  const bool wide_slice = slice_n >= kThreads;   // every thread owns whole bins of the slice
+  if (C > 1 && !wide_slice) {
     for (int i = tid; i < slice_n; i += kThreads) merged[i] = 0u;
   }
   if (tid == 0) sh.res[0] = -1;
   if (C > 1) cluster.sync(); else __syncthreads();   // every CTA's local histogram is complete
   if (tr) FF_TRACE(p, 26);
   if (C > 1) {
-    // nbins loads per CTA in total, all independent: flat index -> (peer, bin of my slice)
+    // nbins loads per CTA in total, all issued before the first use.
     const uint32_t hist_local = smem_addr(hist);
-    const int n_iter = nbins / kThreads;   // 8 for 4096 bins, 2 for 1024, 4 for 2048
+    const int n_iter = nbins / kThreads;   // 16 for 8192 bins, 2 for 1024, 1 for 512, 4 for 2048
     uint32_t v[kMaxBins / kThreads];
+    if (wide_slice) {
+      // load j = m * C + c: bin (tid + m * kThreads) of my slice from peer c; the C loads of a bin
+      // sit next to each other in v[], so a log-step reduction with static indices sums them
+      int log2c = 0;
+      while ((1 << log2c) < C) ++log2c;
 #pragma unroll
-    for (int j = 0; j < kMaxBins / kThreads; ++j) {
-      if (j < n_iter) {
-        const int flat = tid + j * kThreads;
-        const int peer = flat / slice_n;
-        int b = slice_base + (flat - peer * slice_n);
-        if (raw0) b = raw_of_bin(b);
-        v[j] = dsmem_ld_u32(dsmem_addr(hist_local + 4u * static_cast<uint32_t>(b), peer));
+      for (int j = 0; j < kMaxBins / kThreads; ++j) {
+        if (j < n_iter) {
+          int b = slice_base + tid + (j >> log2c) * kThreads;
+          if (raw0) b = raw_of_bin(b);
+          v[j] = dsmem_ld_u32(dsmem_addr(hist_local + 4u * static_cast<uint32_t>(b), j & (C - 1)));
+        } else {
+          v[j] = 0u;
+        }
       }
-    }
 #pragma unroll
-    for (int j = 0; j < kMaxBins / kThreads; ++j) {
-      if (j < n_iter) {
-        const int flat = tid + j * kThreads;
-        if (v[j] != 0u) atomicAdd(&merged[flat % slice_n], v[j]);
+      for (int step = 1; step < kMaxCluster; step <<= 1) {
+        if (step < C) {
+#pragma unroll
+          for (int j = 0; j < kMaxBins / kThreads; j += 2 * step) v[j] += v[j + step];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxBins / kThreads; ++j) {
+        if (j < n_iter && (j & (C - 1)) == 0) merged[tid + (j >> log2c) * kThreads] = v[j];
+      }
+    } else {
+      // narrow slices (later digit levels): flat index -> (peer, bin of my slice), summed with shared atomics
+#pragma unroll
+      for (int j = 0; j < kMaxBins / kThreads; ++j) {
+        if (j < n_iter) {
+          const int flat = tid + j * kThreads;
+          const int peer = flat / slice_n;
+          int b = slice_base + (flat - peer * slice_n);
+          if (raw0) b = raw_of_bin(b);
+          v[j] = dsmem_ld_u32(dsmem_addr(hist_local + 4u * static_cast<uint32_t>(b), peer));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kMaxBins / kThreads; ++j) {
+        if (j < n_iter) {
+          const int flat = tid + j * kThreads;
+          if (v[j] != 0u) atomicAdd(&merged[flat % slice_n], v[j]);
+        }
       }
     }
     __syncthreads();
@@ -578,7 +608,10 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   const int first = tid * per;
   int local = 0;
   if (first < slice_n) {
-    for (int e = 0; e < per; ++e) local += slice_at(first + e);
+    // a thread's `per` consecutive bins are read in a rotated order (the sum does not care)
+    // so that the lanes of a warp hit distinct banks
+    const int rot = per <= 32 ? (tid & 31) / (32 / per) : 0;
+    for (int e = 0; e < per; ++e) local += slice_at(first + ((e + rot) & (per - 1)));
   }
   int total;
   const int excl = block_suffix_exclusive(local, sh.warp_tot, total);
@@ -592,7 +625,8 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   if (publish_remote) {
     for (int c = rank + 1; c < C; ++c) above_slice += sh.slice_tot[c];
   }
-  if (first < slice_n) {
+  // only the one thread whose bins hold the crossing walks them
+  if (first < slice_n && above_slice + excl < r && r <= above_slice + excl + local) {
     int running = above_slice + excl;
     for (int e = per - 1; e >= 0; --e) {
       const int cnt = slice_at(first + e);
@@ -747,7 +781,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   const Chunk chunk = make_chunk(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
 
-  // ---- level 0: 12-bit histogram of the whole chunk -----------------------
+  // ---- level 0: 13-bit histogram of the whole chunk -----------------------
   for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
   TileStream ts;
   ts.src = reinterpret_cast<const float4*>(chunk.abase) + chunk.fb;
@@ -774,7 +808,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   if (HAS_MAP) {
     for_each_in_chunk<true>(
         chunk, [](float) { return true; },
-        [&](float x, int32_t idx) { atomicAdd(&hist[(idx < 0 ? 0u : key_of(x)) >> 20], 1u); });
+        [&](float x, int32_t idx) { atomicAdd(&hist[(idx < 0 ? 0u : key_of(x)) >> kFirstShift], 1u); });
   } else {
     stream_pass(ts, [&](uint32_t tile, int, int units) {
 #pragma unroll
@@ -846,11 +880,11 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     ctx.stage = stage;
     ctx.cand = cand;
     ctx.sh = &sh;
-    // At level 0 "digit >= t" is exactly "value >= value(t << 20)" (unless t lies in
+    // At level 0 "digit >= t" is exactly "value >= value(t << 19)" (unless t lies in
     // the NaN range), so the chunk is swept with float compares only.
     bool swept = false;
-    if (!HAS_MAP && level == 0 && final_level && (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
-      const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
+    if (!HAS_MAP && level == 0 && final_level && (static_cast<uint32_t>(t) << kFirstShift) <= 0xff800000u) {
+      const float vmin = prefilter_value(static_cast<uint32_t>(t) << kFirstShift);
       stream_pass(ts, [&](uint32_t tile, int tt, int units) {
         collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, stage, kSortCap, &sh.stage_count);
       });
@@ -862,18 +896,18 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
       }
       swept = true;
     } else if (!HAS_MAP && !src_is_cand && level == 0 && !final_level &&
-               (static_cast<uint32_t>(t) << 20) <= 0xff800000u) {
+               (static_cast<uint32_t>(t) << kFirstShift) <= 0xff800000u) {
       // Too many elements at or above the threshold bin for the finish: winners
       // (bin > t) go to the stage buffer, the bin's own elements are only counted
       // in the histogram of the next 10 key bits; the chunk is swept once more
       // when that digit's threshold is known.
-      const float vmin = prefilter_value(static_cast<uint32_t>(t) << 20);
+      const float vmin = prefilter_value(static_cast<uint32_t>(t) << kFirstShift);
       auto on_hit = [&](float x, int pos) {
         const uint32_t key = key_of(x);
-        if ((key >> 20) > static_cast<uint32_t>(t)) {
+        if ((key >> kFirstShift) > static_cast<uint32_t>(t)) {
           push_aggregated(stage, &sh.stage_count, kSortCap, make_comp(key, pos));
         } else {
-          atomicAdd(&hist[(key >> 10) & 1023u], 1u);
+          atomicAdd(&hist[(key >> (kFirstShift - 10)) & 1023u], 1u);
         }
       };
       stream_pass(ts, [&](uint32_t tile, int tt, int units) {
@@ -886,13 +920,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
       swept = true;
     } else if (!HAS_MAP && !src_is_cand && level == 1 && final_level) {
       // Second digit resolved: survivors are the elements of bin P whose next 10
-      // bits are >= t, i.e. 22-bit key prefix in [Pn, Pmax]; float pre-filter on the
+      // bits are >= t, i.e. 23-bit key prefix in [Pn, Pmax]; float pre-filter on the
       // lower bound, exact test on the key.
-      const uint32_t key_lo = static_cast<uint32_t>(Pn) << 10;
+      const uint32_t key_lo = static_cast<uint32_t>(Pn) << (kFirstShift - 10);
       const float vmin = prefilter_value(key_lo);
       auto on_hit = [&](float x, int pos) {
         const uint32_t key = key_of(x);
-        const uint32_t pre = key >> 10;
+        const uint32_t pre = key >> (kFirstShift - 10);
         if (pre >= static_cast<uint32_t>(Pn) && pre <= static_cast<uint32_t>(Pmax))
           push_aggregated(stage, &sh.stage_count, kSortCap, make_comp(key, pos));
       };
@@ -1023,7 +1057,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   uint32_t* rankcnt = reinterpret_cast<uint32_t*>(smem + kSmemRing + 48 * 1024);    // per slot: #greater in bucket
   uint32_t* units = reinterpret_cast<uint32_t*>(smem + kSmemRing + 64 * 1024);      // (slot << 8) | chunk, <= 8192
   auto pad = [](uint32_t b) { return b + (b >> 3); };   // 8 consecutive bins per thread -> distinct banks
-  constexpr int kPadBins = kMaxBins + kMaxBins / 8;
+  constexpr int kPadBins = kFinishBins + kFinishBins / 8;
   // bounds of the survivors' composites: exact on the key half, and exact on the
   // index half too when every key is equal (then only the indices separate them)
   uint32_t hmax = 0u, hmin = 0xffffffffu, lmax = 0u, lmin = 0xffffffffu;
@@ -1076,7 +1110,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   __syncthreads();
   FF_TRACE(p, 22);
   {
-    constexpr int per = kMaxBins / kThreads;
+    constexpr int per = kFinishBins / kThreads;
     int local = 0;
 #pragma unroll
     for (int q = 0; q < per; ++q) local += static_cast<int>(fh[pad(tid * per + q)]);
