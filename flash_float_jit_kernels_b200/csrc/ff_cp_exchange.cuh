@@ -1,10 +1,10 @@
 // Context-parallel candidate exchange over peer memory (NVLink / NVSwitch).
 //
 // Every rank owns one allocation holding, for two alternating steps ("parities"),
-// a receive slot per rank and a flag per rank, plus its own send block.  After
-// the shard-local select, cp_push_kernel stores the rank's k candidates per row
-// straight into EVERY peer's receive slot with plain global stores, fences at
-// system scope and raises its flag in that peer's memory; the merge kernel on
+// a receive slot per rank and a flag per rank.  The shard-local select kernel
+// stores the rank's k candidates per row straight into EVERY peer's receive slot
+// with plain global stores as it ranks them; its last CTA fences at system scope
+// and raises the rank's flag in every peer's memory; the merge kernel on
 // each rank polls its own (local) flags with a bounded wait and then reads the
 // candidates from local memory only.  No collective library call, no multicast.
 // The reference has no multi-GPU path; semantics follow fast_topk_v3
@@ -22,46 +22,17 @@
 
 namespace ff {
 
-constexpr int kMaxPeers = 16;
 constexpr unsigned long long kPeerWaitNs = 1000000000ull;   // bounded wait for a peer's flag: one second
 
-struct PeerPtrs {
-  uint32_t* base[kMaxPeers];   // each rank's exchange allocation as mapped in this process
-};
-
 // The step number lives in device memory (word kEpochWord after the flags) so
-// that a captured CUDA graph can be replayed: the push kernel, a single CTA,
-// takes step = counter + 1, copies this rank's candidate block into the slot
-// (step parity, rank) of every peer, raises its flag in every peer to `step`,
-// and only then advances the counter; the merge kernel of the same step, a later
-// launch on the same stream, reads the counter back.
+// that a captured CUDA graph can be replayed.  The select kernel of a step reads
+// step = counter + 1 when it starts, stores its candidates into the slot (step
+// parity, rank) of every peer as it ranks them, and the CTA that finishes last in
+// the whole launch (a done-count next to the counter) raises this rank's flag in
+// every peer to `step` and advances the counter (ff_topk_kernel.cuh).  The merge
+// kernel of the same step, a later launch on the same stream, reads it back.
 constexpr int kEpochWord = 2 * kMaxPeers;
-
-__global__ void __launch_bounds__(1024) cp_push_kernel(const uint32_t* __restrict__ send, PeerPtrs peers,
-                                                       int world, int rank, int words, size_t slot_words,
-                                                       size_t flag_offset) {
-  uint32_t* counter = peers.base[rank] + flag_offset + kEpochWord;
-  const uint32_t step = *counter + 1u;
-  const int parity = static_cast<int>(step & 1u);
-  for (int p = 0; p < world; ++p) {
-    uint32_t* dst = peers.base[p] + (static_cast<size_t>(parity) * world + rank) * slot_words;
-    if ((words & 3) == 0) {
-      const uint4* s4 = reinterpret_cast<const uint4*>(send);
-      uint4* d4 = reinterpret_cast<uint4*>(dst);
-      for (int i = threadIdx.x; i < (words >> 2); i += blockDim.x) d4[i] = s4[i];
-    } else {
-      for (int i = threadIdx.x; i < words; i += blockDim.x) dst[i] = send[i];
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (static_cast<int>(threadIdx.x) < world) {
-    uint32_t* flag = peers.base[threadIdx.x] + flag_offset + static_cast<size_t>(parity) * kMaxPeers + rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) *counter = step;
-}
+constexpr int kPushDoneWord = kEpochWord + 1;
 
 // Polls `n` flags until each has reached `epoch`; returns false if a second passed.
 __device__ __forceinline__ bool wait_for_peers(const uint32_t* flags, int n, uint32_t epoch) {
@@ -102,6 +73,7 @@ struct CpMergeParams {
 };
 
 __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergeParams p) {
+  extern __shared__ uint32_t run_keys[];   // [world][k] monotone keys of this row's runs
   __shared__ int n_valid[kMaxPeers];
   const int row = blockIdx.y;
   const uint32_t step = p.flags[kEpochWord];
@@ -118,10 +90,14 @@ __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergePara
   }
   const uint32_t* base = p.recv_even + parity * p.parity_stride;
   const size_t plane = static_cast<size_t>(p.B) * k;
-  auto val_of = [&](int q, int j) { return base[static_cast<size_t>(q) * p.slot_words + static_cast<size_t>(row) * k + j]; };
   auto idx_of = [&](int q, int j) {
     return static_cast<int32_t>(base[static_cast<size_t>(q) * p.slot_words + plane + static_cast<size_t>(row) * k + j]);
   };
+  // stage the keys of all runs in shared memory: the binary searches then never leave the SM
+  for (int i = threadIdx.x; i < p.world * k; i += blockDim.x) {
+    const int q = i / k;
+    run_keys[i] = key_of_bits(base[static_cast<size_t>(q) * p.slot_words + static_cast<size_t>(row) * k + (i - q * k)]);
+  }
   if (static_cast<int>(threadIdx.x) < p.world) {   // valid entries of run q: unused slots (index -1) sit at its tail
     const int q = threadIdx.x;
     int lo = 0, hi = k;
@@ -137,14 +113,15 @@ __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergePara
   const int run = c / k;
   const int j = c - run * k;
   if (j >= n_valid[run]) return;
-  const uint32_t key = key_of_bits(val_of(run, j));
+  const uint32_t key = run_keys[c];
   int rank = j;
   for (int q = 0; q < p.world; ++q) {
     if (q == run) continue;
+    const uint32_t* keys = run_keys + q * k;
     int lo = 0, hi = n_valid[q];
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
-      const uint32_t kq = key_of_bits(val_of(q, mid));
+      const uint32_t kq = keys[mid];
       const bool before = q < run ? kq >= key : kq > key;
       if (before) lo = mid + 1; else hi = mid;
     }

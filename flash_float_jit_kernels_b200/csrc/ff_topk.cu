@@ -92,6 +92,9 @@ void init_device(int device) {
   if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true>);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(ff::cp_merge_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ff::kMaxPeers * ff::kMaxK * static_cast<int>(sizeof(uint32_t)));
   if (e == cudaSuccess) {
     g_max_cluster[device] = max_cluster_for(ff::topk_cluster_kernel<false>);
     for (int i = 0; i < 5; ++i)
@@ -555,20 +558,40 @@ int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const
   FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
   for (int p = 0; p < ex->world; ++p)
     if (ex->peer[p] == nullptr) return fail(FF_ERR_NULL, "exchange: a peer is not mapped yet");
-  uint32_t* send = ex->base + ex->send_offset;
-  const size_t plane = static_cast<size_t>(ex->B) * ex->k;
-  int rc = ff_topk_cp_local(scores, row_stride, lengths, reinterpret_cast<int32_t*>(send + plane),
-                            reinterpret_cast<float*>(send), ex->B, L_width, ex->k, shard_offset, workspace,
-                            workspace_bytes, status, stream);
+  // One launch: the shard-local select writes its k candidates per row straight into every
+  // peer's receive slot and the last CTA raises the flags (no separate push kernel).
+  int rc = check_common(ex->B, L_width, ex->k);
   if (rc != 0) return rc;
-  ff::PeerPtrs peers;
-  for (int p = 0; p < ff::kMaxPeers; ++p) peers.base[p] = static_cast<uint32_t*>(p < ex->world ? ex->peer[p] : nullptr);
-  ff::cp_push_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      send, peers, ex->world, ex->rank, static_cast<int>(2 * plane), ex->slot_words, ex->flag_offset);
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail_cuda(e, "cp_push_kernel");
-  g_launches.fetch_add(1, std::memory_order_relaxed);
-  return 0;
+  if (scores == nullptr || lengths == nullptr) return fail(FF_ERR_NULL, "scores and lengths must not be NULL");
+  if (shard_offset < 0 || shard_offset + L_width > 0x7fffffffLL)
+    return fail(FF_ERR_TOO_LARGE, "shard_offset + L_width exceeds int32 indices");
+  int device = 0;
+  rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  ff::TopkParams p = {};
+  p.scores = scores;
+  p.row_stride = row_stride;
+  p.lengths = lengths;
+  p.out_idx = reinterpret_cast<int32_t*>(ex->base + ex->send_offset);   // unused in push mode
+  p.out_val = reinterpret_cast<float*>(ex->base + ex->send_offset);     // non-null marks candidate mode
+  p.B = ex->B;
+  p.k = ex->k;
+  p.L_width = L_width;
+  p.shard_offset = shard_offset;
+  p.fixed_len = -1;
+  p.status = status;
+  for (int q = 0; q < ff::kMaxPeers; ++q)
+    p.push_peers.base[q] = static_cast<uint32_t*>(q < ex->world ? ex->peer[q] : nullptr);
+  p.push_world = ex->world;
+  p.push_rank = ex->rank;
+  p.push_slot_words = static_cast<int64_t>(ex->slot_words);
+  p.push_flag_offset = static_cast<int64_t>(ex->flag_offset);
+  int cluster = choose_cluster(device, ex->B, L_width, ex->k);
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
+    p.groups = choose_groups(device, ex->B, L_width, workspace_bytes, &cluster);
+    p.workspace = static_cast<uint32_t*>(workspace);
+  }
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
 }
 
 int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx, int32_t* status,
@@ -588,7 +611,8 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
   p.k = ex->k;
   const int n_cand = ex->world * ex->k;
   const dim3 grid((n_cand + 1023) / 1024, ex->B, 1);
-  ff::cp_merge_sorted_kernel<<<grid, 1024, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const size_t key_bytes = static_cast<size_t>(n_cand) * sizeof(uint32_t);   // <= 128 KiB
+  ff::cp_merge_sorted_kernel<<<grid, 1024, key_bytes, static_cast<cudaStream_t>(stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "cp_merge_sorted_kernel");
   g_launches.fetch_add(1, std::memory_order_relaxed);

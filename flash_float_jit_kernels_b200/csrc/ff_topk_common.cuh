@@ -55,6 +55,11 @@ __device__ __forceinline__ int32_t comp_index(uint64_t c) {
 }
 __device__ __forceinline__ uint32_t comp_key(uint64_t c) { return static_cast<uint32_t>(c >> 32); }
 
+constexpr int kMaxPeers = 16;
+struct PeerPtrs {
+  uint32_t* base[kMaxPeers];   // each rank's exchange allocation as mapped in this process
+};
+
 struct TopkParams {
   const float* scores;         // [B, row_stride]
   int64_t row_stride;
@@ -82,6 +87,11 @@ struct TopkParams {
   const uint32_t* wait_flags;  // merge mode: [2][16] flags raised by the peers' pushes, step counter after them; or null
   int32_t wait_n;              // number of peers
   int64_t parity_stride;       // elements between the receive buffers of even and odd steps
+  PeerPtrs push_peers;         // context-parallel send: results go to these exchange buffers
+  int32_t push_world;          // > 0 switches the push on
+  int32_t push_rank;
+  int64_t push_slot_words;
+  int64_t push_flag_offset;
   unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
 

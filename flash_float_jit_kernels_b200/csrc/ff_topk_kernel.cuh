@@ -653,8 +653,22 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
 }
 
 // Writes output slot j of `row` from a window-relative index (or -1) and key.
-__device__ __forceinline__ void emit(const TopkParams& p, int row, int j, int32_t idx, uint32_t key,
-                                     bool is_map, int table_row) {
+// In push mode (context-parallel send) the slot is not written locally at all: the (value,
+// global index) pair goes straight into this rank's slot of every peer's receive buffer.
+__device__ __forceinline__ void emit(const TopkParams& p, int64_t push_off, int row, int j, int32_t idx,
+                                     uint32_t key, bool is_map, int table_row) {
+  if (p.push_world > 0) {
+    const uint32_t vbits = idx < 0 ? 0xff800000u : bits_of_key(key);
+    const uint32_t gidx = idx < 0 ? 0xffffffffu : static_cast<uint32_t>(idx + p.shard_offset);
+    const size_t at = static_cast<size_t>(row) * p.k + j;
+    const size_t plane = static_cast<size_t>(p.B) * p.k;
+    for (int q = 0; q < p.push_world; ++q) {
+      uint32_t* slot = p.push_peers.base[q] + push_off;
+      slot[at] = vbits;
+      slot[plane + at] = gidx;
+    }
+    return;
+  }
   int32_t o;
   if (idx < 0) {
     o = -1;
@@ -680,9 +694,8 @@ __device__ __forceinline__ float prefilter_value(uint32_t key_lo) {
 }
 
 template <bool HAS_MAP>
-__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ ClusterShared sh;
+__device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
+                                              int64_t push_off) {
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
   uint32_t* merged = reinterpret_cast<uint32_t*>(smem + kSmemStage);
@@ -751,13 +764,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
       __syncthreads();
       for (int j = tid; j < k; j += kThreads) {
         if (j >= len) {
-          emit(p, row, j, -1, 0u, false, table_row);
+          emit(p, push_off, row, j, -1, 0u, false, table_row);
           continue;
         }
         const uint64_t c = stage[j];
         int pos = 0;
         for (int q = 0; q < len; ++q) pos += stage[q] > c ? 1 : 0;
-        emit(p, row, pos, comp_index(c), comp_key(c), false, table_row);
+        emit(p, push_off, row, pos, comp_index(c), comp_key(c), false, table_row);
       }
       return;
     }
@@ -766,13 +779,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
         // no more candidates than k slots: pass them through in position order
         const int64_t a = j < len ? seg_addr(j, p.seg_len, p.seg_stride) : 0;
         const int32_t idx = j < len ? imap[a] : -1;
-        emit(p, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
+        emit(p, push_off, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
       } else {
         const int n = HAS_MAP ? glen : len;
         const bool v = j < n;
         uint32_t key = 0u;
         if (v && !HAS_MAP && p.out_val != nullptr) key = key_of(rowp[j]);
-        emit(p, row, j, v ? j : -1, key, HAS_MAP, table_row);
+        emit(p, push_off, row, j, v ? j : -1, key, HAS_MAP, table_row);
       }
     }
     return;
@@ -1033,7 +1046,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   if (!ok) {
     if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
     if (my_share == 0) {
-      for (int j = tid; j < k; j += kThreads) emit(p, row, j, -1, 0u, HAS_MAP, table_row);
+      for (int j = tid; j < k; j += kThreads) emit(p, push_off, row, j, -1, 0u, HAS_MAP, table_row);
     }
     return;
   }
@@ -1203,9 +1216,49 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
-    if (pos < k) emit(p, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (pos < k) emit(p, push_off, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
   }
   FF_TRACE(p, 25);
+}
+
+template <bool HAS_MAP>
+__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ ClusterShared sh;
+  // Context-parallel send: this launch also delivers its result to the peers.  The step number is
+  // read from device memory (graph replays), the slot it selects is fixed for the whole launch.
+  uint32_t step = 0;
+  int64_t push_off = 0;
+  uint32_t* mine = nullptr;
+  if (!HAS_MAP && p.push_world > 0) {
+    mine = p.push_peers.base[p.push_rank] + p.push_flag_offset;
+    step = *reinterpret_cast<volatile uint32_t*>(mine + kEpochWord) + 1u;
+    push_off = (static_cast<int64_t>(step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
+  }
+  topk_row_body<HAS_MAP>(p, smem, sh, push_off);
+  if (!HAS_MAP && p.push_world > 0) {
+    // Every thread publishes its remote stores; the CTA that finishes last in the whole launch
+    // raises this rank's flag in every peer and advances the step counter.
+    __syncthreads();
+    bool last = false;
+    if (threadIdx.x == 0) {
+      __threadfence();          // device scope: cumulative over the CTA's stores ordered before the barrier
+      last = atomicAdd(mine + kPushDoneWord, 1u) == gridDim.x - 1u;
+    }
+    if (last) {
+      // the release chain of every CTA ends here; one system-scope fence covers all their stores
+      __threadfence_system();
+      const int parity = static_cast<int>(step & 1u);
+      for (int q = 0; q < p.push_world; ++q) {
+        uint32_t* flag = p.push_peers.base[q] + p.push_flag_offset + static_cast<size_t>(parity) * kMaxPeers +
+                         p.push_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+      }
+      mine[kPushDoneWord] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(mine + kEpochWord) = step;
+    }
+  }
 }
 
 }  // namespace ff
