@@ -325,6 +325,8 @@ __device__ __forceinline__ float4 lds_f4(uint32_t addr) {
 // sign-magnitude order and the monotone bin order when the histogram is read.
 __device__ __forceinline__ uint32_t raw_digit(float x) { return __float_as_uint(__fadd_rn(x, 0.0f)) >> kFirstShift; }
 __device__ __forceinline__ int raw_of_bin(int m) { return m ^ ((m & (kMaxBins >> 1)) ? (kMaxBins >> 1) : (kMaxBins - 1)); }
+// the same translation for groups of bins (n groups, n a power of two)
+__device__ __forceinline__ int raw_of_group(int m, int n) { return m ^ ((m & (n >> 1)) ? (n >> 1) : (n - 1)); }
 
 // Key and composite of one element; ignored merge entries (index < 0) map to 0.
 template <bool HAS_MAP>
@@ -335,7 +337,8 @@ __device__ __forceinline__ uint64_t comp_of(float x, int32_t idx) {
 
 struct ClusterShared {
   int slice_tot[kMaxCluster];
-  int res[4];        // threshold digit, count above it, count in it, (unused)
+  int res[4];        // threshold digit, count above it, count in it, coarse bin (two-step merge)
+  uint32_t coarse[256];   // this CTA's histogram summed in groups of 32 bins, raw order (read by peers)
   int warp_tot[kWarps];
   int stage_count;
   int sort_count;
@@ -652,6 +655,95 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
   if (publish_remote) cluster.sync(); else __syncthreads();   // the threshold triple has arrived everywhere
 }
 
+// First-digit merge for a row inside ONE cluster, without any exchange of partial
+// results: after a single cluster barrier every CTA (1) reads a 256-bin coarse view
+// (sums of 32 bins) of every peer's histogram over DSMEM and finds the coarse bin
+// that holds the crossing, then (2) reads that coarse bin's 32 fine bins from every
+// peer and finds the threshold digit.  Every CTA computes the same triple, so the
+// two cluster barriers and the slice-total / result stores of merge_and_scan are
+// not needed, and a CTA issues 8 + 1 remote loads per thread instead of 16.
+// `scratch` needs 512 + 32 * C words.  The peers' histograms must stay untouched
+// until the next cluster barrier.
+__device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C, uint32_t* hist,
+                                               uint32_t* scratch, int r, ClusterShared& sh,
+                                               const TopkParams& p) {
+  constexpr int kCoarse = 256;
+  constexpr int kFinePer = kMaxBins / kCoarse;   // 32
+  static_assert(kFinePer == 32 && kThreads == 2 * kCoarse, "layout of the two-step merge");
+  const int tid = threadIdx.x;
+  uint32_t* gcoarse = scratch;         // [2][256] sums over one half of the peers each
+  uint32_t* gfine = scratch + 512;     // [C][32]
+  {
+    // local coarse sums: 16 consecutive words per thread, read in a rotated order (distinct banks)
+    const int rot = (tid & 31) >> 1;
+    uint32_t sum = 0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) sum += hist[16 * tid + ((e + rot) & 15)];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    if ((tid & 1) == 0) sh.coarse[tid >> 1] = sum;
+  }
+  if (tid == 0) sh.res[0] = -1;
+  cluster.sync();   // every CTA's histogram and coarse sums are complete
+  FF_TRACE(p, 26);
+  {
+    const int g = tid & (kCoarse - 1);
+    const int half = tid >> 8;
+    const int per_half = C >> 1;
+    const uint32_t a = smem_addr(&sh.coarse[g]);
+    uint32_t v[kMaxCluster / 2];
+#pragma unroll
+    for (int j = 0; j < kMaxCluster / 2; ++j) v[j] = j < per_half ? dsmem_ld_u32(dsmem_addr(a, half * per_half + j)) : 0u;
+    uint32_t sum = 0;
+#pragma unroll
+    for (int j = 0; j < kMaxCluster / 2; ++j) sum += v[j];
+    gcoarse[half * kCoarse + g] = sum;
+  }
+  __syncthreads();
+  FF_TRACE(p, 27);
+  int val = 0;
+  if (tid < kCoarse) {
+    const int g = raw_of_group(tid, kCoarse);   // coarse bins in monotone order
+    val = static_cast<int>(gcoarse[g] + gcoarse[kCoarse + g]);
+  }
+  int total;
+  const int excl = block_suffix_exclusive(val, sh.warp_tot, total);
+  if (tid < kCoarse && excl < r && r <= excl + val) {
+    sh.res[3] = tid;
+    sh.res[1] = excl;
+  }
+  __syncthreads();
+  FF_TRACE(p, 28);
+  if (total < r) return;   // no crossing: res[0] stays -1 (uniform over the cluster)
+  const int cbin = sh.res[3];
+  const int above_c = sh.res[1];
+  if (tid < kFinePer * C) {
+    const int f = tid & (kFinePer - 1);
+    const int peer = tid >> 5;
+    const int b = raw_of_bin(cbin * kFinePer + f);
+    gfine[tid] = dsmem_ld_u32(dsmem_addr(smem_addr(hist) + 4u * static_cast<uint32_t>(b), peer));
+  }
+  __syncthreads();
+  FF_TRACE(p, 29);
+  if (tid < 32) {
+    int cnt = 0;
+    for (int c = 0; c < C; ++c) cnt += static_cast<int>(gfine[c * kFinePer + tid]);
+    int incl = cnt;   // inclusive suffix sum over the lanes (higher lane = larger values)
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_down_sync(0xffffffffu, incl, off);
+      if (tid + off < 32) incl += t;
+    }
+    const int above = above_c + incl - cnt;
+    if (above < r && r <= above + cnt) {
+      sh.res[1] = above;
+      sh.res[2] = cnt;
+      sh.res[0] = cbin * kFinePer + tid;
+    }
+  }
+  __syncthreads();
+  FF_TRACE(p, 30);
+}
+
 // Writes output slot j of `row` from a window-relative index (or -1) and key.
 // In push mode (context-parallel send) the slot is not written locally at all: the (value,
 // global index) pair goes straight into this rank's slot of every peer's receive buffer.
@@ -856,8 +948,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const int bits = level_bits(level);
     const int shift = level_shift(level);
     const bool raw0 = !HAS_MAP && level == 0;
-    merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0, G, ws, level,
-                   ts.timed_out);
+    const bool two_step = raw0 && G == 1 && C > 1;
+    if (two_step) {
+      merge_two_step(cluster, C, hist, merged, r, sh, p);
+    } else {
+      merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0, G, ws, level,
+                     ts.timed_out);
+    }
     levels_used = level + 1;
     FF_TRACE(p, 2 + 3 * level);
     const int t = sh.res[0];
@@ -877,6 +974,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint32_t nmask = final_level ? 0u : ((1u << level_bits(level + 1)) - 1u);
     __syncthreads();
     if (!final_level) {
+      if (two_step) cluster.sync();   // peers may still be reading this histogram (no barrier ended the merge)
       for (int i = tid; i < (1 << level_bits(level + 1)); i += kThreads) hist[i] = 0u;
     }
     __syncthreads();
