@@ -153,7 +153,7 @@ int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
 // all SMs sweep them; that needs the caller's zero-filled workspace and a
 // cooperative launch (all CTAs of a row wait for each other through global
 // memory).  Returns the number of clusters per row and may lower `cluster`.
-constexpr int64_t kGroupMinWidth = 524288;
+constexpr int64_t kGroupMinWidth = 786432;
 constexpr int kGroupCluster = 8;
 int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes, int* cluster) {
   int g = g_groups_override.load();

@@ -481,9 +481,11 @@ __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_un
 //   [0, 6)   arrivals at the histogram barrier of digit level 0..5
 //   [6]      arrivals at the survivor barrier      [7] CTAs that are done
 //   [8]      survivors appended so far
-//   [64, 64 + 6 * 8192)          one 8192-bin global histogram per digit level
-//   [64 + 6 * 8192, + 2 * 4096)  survivor list (4096 x 64-bit composites)
-constexpr int kWsHeaderWords = 64;
+//   [64, 320) first digit level only: the row's histogram summed in groups of 32 bins
+//   [320, 320 + 6 * 8192)        one 8192-bin global histogram per digit level
+//   [320 + 6 * 8192, + 2 * 4096) survivor list (4096 x 64-bit composites)
+constexpr int kWsCoarseWord = 64;            // 256 coarse bins (sums of 32 first-level bins) of the row
+constexpr int kWsHeaderWords = 64 + 256;
 constexpr int kWsHistWords = kNumLevels * kMaxBins;
 constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kSortCap;
 constexpr int kSpinLimit = 1 << 21;   // bounded polling of a row barrier (about a second)
@@ -599,7 +601,48 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
       const int v = slice_at(i);
       if (v != 0) atomicAdd(&gh[slice_base + i], static_cast<uint32_t>(v));
     }
+    // first level: also a coarse view (groups of 32 bins), so that after the barrier a CTA reads
+    // 256 + 32 words instead of the whole histogram
+    const bool two_step = level == 0 && nbins == kMaxBins;
+    if (two_step) {
+      const int lane = tid & 31;
+      for (int g = tid >> 5; g < slice_n / 32; g += kWarps) {
+        const uint32_t sum = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(slice_at(32 * g + lane)));
+        if (lane == 0 && sum != 0u) atomicAdd(ws + kWsCoarseWord + slice_base / 32 + g, sum);
+      }
+    }
     if (!row_barrier(ws + level, static_cast<uint32_t>(G * C), &sh.flag)) timed_out = true;
+    if (two_step) {
+      const int val = tid < 256 ? static_cast<int>(__ldcg(ws + kWsCoarseWord + tid)) : 0;
+      int total;
+      const int excl = block_suffix_exclusive(val, sh.warp_tot, total);
+      if (tid < 256 && excl < r && r <= excl + val) {
+        sh.res[3] = tid;
+        sh.res[1] = excl;
+      }
+      __syncthreads();
+      if (total < r) return;   // no crossing: res[0] stays -1 for every CTA of the row
+      const int cbin = sh.res[3];
+      const int above_c = sh.res[1];
+      __syncthreads();
+      if (tid < 32) {
+        const int cnt = static_cast<int>(__ldcg(&gh[cbin * 32 + tid]));
+        int incl = cnt;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int t = __shfl_down_sync(0xffffffffu, incl, off);
+          if (tid + off < 32) incl += t;
+        }
+        const int above = above_c + incl - cnt;
+        if (above < r && r <= above + cnt) {
+          sh.res[1] = above;
+          sh.res[2] = cnt;
+          sh.res[0] = cbin * 32 + tid;
+        }
+      }
+      __syncthreads();
+      return;
+    }
     for (int i = tid; i < nbins; i += kThreads) merged[i] = __ldcg(&gh[i]);
     __syncthreads();
     from_merged = true;
