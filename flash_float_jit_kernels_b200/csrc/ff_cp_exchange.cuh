@@ -1,18 +1,20 @@
 // Context-parallel candidate exchange over peer memory (NVLink / NVSwitch).
 //
 // Every rank owns one allocation holding, for two alternating steps ("parities"),
-// a receive slot per rank and a flag per rank.  The shard-local select kernel
-// stores the rank's k candidates per row straight into EVERY peer's receive slot
-// with plain global stores as it ranks them; its last CTA fences at system scope
-// and raises the rank's flag in every peer's memory; the merge kernel on
-// each rank polls its own (local) flags with a bounded wait and then reads the
-// candidates from local memory only.  No collective library call, no multicast.
+// a receive slot per rank.  A slot is two planes of 8-byte entries, one entry per
+// (row, position): {value bits, step} and {global index, step}.  The shard-local
+// select kernel stores each of its k candidates per row straight into EVERY
+// peer's slot as it ranks them, one 8-byte store per entry.  An 8-byte aligned
+// store arrives whole, so the step number inside the entry is its own "valid"
+// mark: the receiver polls an entry until it carries the current step (bounded
+// wait).  No fence, no flag, no collective library call, no multicast; the
+// receiver reads local memory only.
 // The reference has no multi-GPU path; semantics follow fast_topk_v3
 // (jit_kernel/topk_indexer.py:109) on the unsharded row.
 //
 // Two parities suffice: a rank can only be one step ahead of a peer, because its
-// merge of step s needs that peer's push of step s, which the peer issues after
-// its own merge of step s-1 on the same stream.
+// merge of step s needs that peer's entries of step s, which the peer stores
+// after its own merge of step s-1 on the same stream.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -22,103 +24,110 @@
 
 namespace ff {
 
-constexpr unsigned long long kPeerWaitNs = 1000000000ull;   // bounded wait for a peer's flag: one second
+constexpr unsigned long long kPeerWaitNs = 1000000000ull;   // bounded wait for a peer's entries: one second
 
-// The step number lives in device memory (word kEpochWord after the flags) so
-// that a captured CUDA graph can be replayed.  The select kernel of a step reads
-// step = counter + 1 when it starts, stores its candidates into the slot (step
-// parity, rank) of every peer as it ranks them, and the CTA that finishes last in
-// the whole launch (a done-count next to the counter) raises this rank's flag in
-// every peer to `step` and advances the counter (ff_topk_kernel.cuh).  The merge
-// kernel of the same step, a later launch on the same stream, reads it back.
-constexpr int kEpochWord = 2 * kMaxPeers;
-constexpr int kPushDoneWord = kEpochWord + 1;
+// Control words behind the receive slots.  The step number lives in device
+// memory so that a captured CUDA graph can be replayed: every CTA of a step's
+// select kernel reads step = counter + 1 when it starts and counts itself in
+// kPushDoneWord once it has; the CTA that counts last advances the counter (no
+// CTA of the launch reads it again).  A merge kernel launched after the select
+// reads the advanced counter back.
+constexpr int kEpochWord = 0;
+constexpr int kPushDoneWord = 1;
+constexpr int kCtrlWords = 64;
 
-// Polls `n` flags until each has reached `epoch`; returns false if a second passed.
-__device__ __forceinline__ bool wait_for_peers(const uint32_t* flags, int n, uint32_t epoch) {
+// A slot position that holds no candidate carries this value pattern (a NaN the select
+// never emits: it writes NaN as 0x7fffffff); the merge turns it into key 0, below every real key.
+constexpr uint32_t kNoCandidateBits = 0xffffffffu;
+__device__ __forceinline__ uint32_t run_key_of_bits(uint32_t bits) {
+  return bits == kNoCandidateBits ? 0u : key_of_bits(bits);
+}
+
+__device__ __forceinline__ void st_entry(uint32_t* entry, uint32_t payload, uint32_t step) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(entry), "r"(payload), "r"(step) : "memory");
+}
+__device__ __forceinline__ uint2 ld_entry(const uint32_t* entry) {
+  uint2 e;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(entry) : "memory");
+  return e;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Polls the entry until it carries `step`; gives up (ok = false, payload = no candidate) when
+// more than kPeerWaitNs have passed since t0.
+__device__ __forceinline__ uint32_t await_entry(const uint32_t* entry, uint2 first, uint32_t step,
+                                                unsigned long long t0, bool& ok) {
+  uint2 e = first;
+  while (e.y != step) {
+    if (global_ns() - t0 > kPeerWaitNs) {
+      ok = false;
+      return kNoCandidateBits;
+    }
+    e = ld_entry(entry);
+  }
+  return e.x;
+}
+
+// Where the receive slots of one step and one row are.
+struct RunSource {
+  const uint32_t* base;   // this rank's receive area of the step's parity: [world][slot_words]
+  int64_t slot_words;     // per rank: value plane then index plane, 2 words per (row, position)
+  int64_t plane_words;    // 2 * B * k
+  int64_t row_words;      // 2 * row * k
+  __device__ __forceinline__ const uint32_t* value_entry(int q, int j) const {
+    return base + q * slot_words + row_words + 2 * j;
+  }
+  __device__ __forceinline__ const uint32_t* index_entry(int q, int j) const {
+    return base + q * slot_words + plane_words + row_words + 2 * j;
+  }
+};
+
+// Waits for the value entries of all world x k candidates of the row and stages their
+// monotone keys in run_keys[world][k] (shared memory).  Four entries per thread are in
+// flight at a time.  Returns false (uniformly) if an entry did not arrive in time.
+__device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, int k, uint32_t step,
+                                               uint32_t* run_keys) {
+  const int n_cand = world * k;
+  const int nthreads = static_cast<int>(blockDim.x);
+  const unsigned long long t0 = global_ns();
   bool ok = true;
-  if (static_cast<int>(threadIdx.x) < n) {
-    unsigned long long t0;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-    for (;;) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + threadIdx.x) : "memory");
-      if (static_cast<int32_t>(v - epoch) >= 0) break;
-      unsigned long long t1;
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-      if (t1 - t0 > kPeerWaitNs) {
-        ok = false;
-        break;
+  for (int i0 = threadIdx.x; i0 < n_cand; i0 += 4 * nthreads) {
+    const uint32_t* ptr[4];
+    uint2 e[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * nthreads;
+      if (i < n_cand) {
+        const int q = i / k;
+        ptr[u] = src.value_entry(q, i - q * k);
+        e[u] = ld_entry(ptr[u]);
       }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = i0 + u * nthreads;
+      if (i < n_cand) run_keys[i] = run_key_of_bits(await_entry(ptr[u], e[u], step, t0, ok));
     }
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-// Merge-select for the exchange path.  Every rank's block is a run already in
-// canonical order (value desc, index asc) and the shards are contiguous in rank
-// order, so the global rank of candidate j of run p is
-//   j + sum over q < p of #(key_q >= key) + sum over q > p of #(key_q > key),
-// each term one binary search on the keys of run q.  One thread per candidate
-// writes its index straight to its output slot; nothing is sorted or staged.
-struct CpMergeParams {
-  const uint32_t* recv_even;   // receive buffer of even steps: [world][slot_words]
-  int64_t parity_stride;       // words to the buffer of odd steps
-  int64_t slot_words;          // per rank: value plane [B*k], index plane [B*k]
-  const uint32_t* flags;       // [2][kMaxPeers] flags, then the step counter
-  const int32_t* lengths;      // global row lengths
-  int32_t* out_idx;            // [B, k]
-  int32_t* status;
-  int world, B, k;
-};
-
-__global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergeParams p) {
-  extern __shared__ uint32_t run_keys[];   // [world][k] monotone keys of this row's runs
-  __shared__ int n_valid[kMaxPeers];
-  const int row = blockIdx.y;
-  const uint32_t step = p.flags[kEpochWord];
-  const int parity = static_cast<int>(step & 1u);
-  if (!wait_for_peers(p.flags + parity * kMaxPeers, p.world, step) && p.status != nullptr && threadIdx.x == 0)
-    atomicOr(p.status, 2);
-  const int k = p.k;
-  const int glen = p.lengths[row];
-  if (glen <= k) {   // short row: identity order, as everywhere else
-    if (blockIdx.x == 0) {
-      for (int j = threadIdx.x; j < k; j += blockDim.x) p.out_idx[static_cast<int64_t>(row) * k + j] = j < glen ? j : -1;
-    }
-    return;
-  }
-  const uint32_t* base = p.recv_even + parity * p.parity_stride;
-  const size_t plane = static_cast<size_t>(p.B) * k;
-  auto idx_of = [&](int q, int j) {
-    return static_cast<int32_t>(base[static_cast<size_t>(q) * p.slot_words + plane + static_cast<size_t>(row) * k + j]);
-  };
-  // stage the keys of all runs in shared memory: the binary searches then never leave the SM
-  for (int i = threadIdx.x; i < p.world * k; i += blockDim.x) {
-    const int q = i / k;
-    run_keys[i] = key_of_bits(base[static_cast<size_t>(q) * p.slot_words + static_cast<size_t>(row) * k + (i - q * k)]);
-  }
-  if (static_cast<int>(threadIdx.x) < p.world) {   // valid entries of run q: unused slots (index -1) sit at its tail
-    const int q = threadIdx.x;
-    int lo = 0, hi = k;
-    while (lo < hi) {
-      const int mid = (lo + hi) >> 1;
-      if (idx_of(q, mid) >= 0) lo = mid + 1; else hi = mid;
-    }
-    n_valid[q] = lo;
-  }
-  __syncthreads();
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= p.world * k) return;
-  const int run = c / k;
-  const int j = c - run * k;
-  if (j >= n_valid[run]) return;
-  const uint32_t key = run_keys[c];
+// Global rank of candidate j (key `key`) of run `run` among `world` runs of k keys each, all
+// in shared memory in descending order with key 0 in unused tail positions.  Every rank's run
+// is in canonical order (value desc, index asc) and the shards are contiguous in rank order, so
+//   rank = j + sum over q < run of #(key_q >= key) + sum over q > run of #(key_q > key),
+// each term one binary search.
+__device__ __forceinline__ int rank_among_runs(const uint32_t* run_keys, int world, int k, int run, int j,
+                                               uint32_t key) {
   int rank = j;
-  for (int q = 0; q < p.world; ++q) {
+  for (int q = 0; q < world; ++q) {
     if (q == run) continue;
     const uint32_t* keys = run_keys + q * k;
-    int lo = 0, hi = n_valid[q];
+    int lo = 0, hi = k;
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
       const uint32_t kq = keys[mid];
@@ -127,7 +136,66 @@ __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergePara
     }
     rank += lo;
   }
-  if (rank < k) p.out_idx[static_cast<int64_t>(row) * k + rank] = idx_of(run, j);
+  return rank;
+}
+
+// Ranks candidates [begin, end) of the row's world x k and writes each winner's global
+// index straight to its output position.  run_keys must be staged.  Returns false if an index
+// entry did not arrive in time (thread-local).
+__device__ __forceinline__ bool rank_and_write(const RunSource& src, const uint32_t* run_keys, int world, int k,
+                                               uint32_t step, int begin, int end, int32_t* out_row) {
+  const unsigned long long t0 = global_ns();
+  bool ok = true;
+  for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
+    const uint32_t key = run_keys[c];
+    if (key == 0u) continue;   // no candidate here
+    const int run = c / k;
+    const int j = c - run * k;
+    const uint32_t* ie = src.index_entry(run, j);
+    const uint2 first = ld_entry(ie);
+    const int rank = rank_among_runs(run_keys, world, k, run, j, key);
+    const uint32_t gidx = await_entry(ie, first, step, t0, ok);
+    if (rank < k && ok) out_row[rank] = static_cast<int32_t>(gidx);
+  }
+  return ok;
+}
+
+// Merge-select as a launch of its own (after the select kernel on the same stream): used when
+// the select's CTAs cannot all be resident at once, and by tests that play several ranks on one
+// GPU.  grid = (ceil(world * k / 1024), B); dynamic shared memory world * k * 4 bytes.
+struct CpMergeParams {
+  const uint32_t* recv_even;   // receive area of even steps: [world][slot_words]
+  int64_t parity_words;        // words to the area of odd steps
+  int64_t slot_words;
+  const uint32_t* ctrl;        // control words (step counter)
+  const int32_t* lengths;      // global row lengths
+  int32_t* out_idx;            // [B, k]
+  int32_t* status;
+  int world, B, k;
+};
+
+__global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergeParams p) {
+  extern __shared__ uint32_t run_keys[];   // [world][k] monotone keys of this row's runs
+  const int row = blockIdx.y;
+  const uint32_t step = p.ctrl[kEpochWord];   // advanced by this step's select kernel
+  const int k = p.k;
+  const int glen = p.lengths[row];
+  if (glen <= k) {   // short row: identity order, as everywhere else
+    if (blockIdx.x == 0) {
+      for (int j = threadIdx.x; j < k; j += blockDim.x) p.out_idx[static_cast<int64_t>(row) * k + j] = j < glen ? j : -1;
+    }
+    return;
+  }
+  RunSource src;
+  src.base = p.recv_even + static_cast<int64_t>(step & 1u) * p.parity_words;
+  src.slot_words = p.slot_words;
+  src.plane_words = 2 * static_cast<int64_t>(p.B) * k;
+  src.row_words = 2 * static_cast<int64_t>(row) * k;
+  bool ok = stage_run_keys(src, p.world, k, step, run_keys);
+  const int begin = blockIdx.x * blockDim.x;
+  const int end = min(p.world * k, begin + static_cast<int>(blockDim.x));
+  ok = rank_and_write(src, run_keys, p.world, k, step, begin, end, p.out_idx + static_cast<int64_t>(row) * k) && ok;
+  if (!ok && p.status != nullptr) atomicOr(p.status, 2);
 }
 
 }  // namespace ff

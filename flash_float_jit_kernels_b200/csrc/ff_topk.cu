@@ -119,11 +119,6 @@ int ensure_init(int* device_out) {
   return 0;
 }
 
-int pow2_ceil(int64_t v) {
-  int p = 1;
-  while (p < v && p < (1 << 30)) p <<= 1;
-  return p;
-}
 
 // Cluster size per row.  One CTA sweeps about 16 Ki scores; the cluster grows
 // with the row up to the largest size the device can schedule, but not beyond
@@ -455,8 +450,8 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
 
 struct FfCpExchange {
   int world, rank, B, k, device;
-  size_t slot_words;     // one rank's candidate block: value plane then index plane, 2*B*k words rounded up to 4
-  size_t flag_offset;    // words from the allocation's start to the flags
+  size_t slot_words;     // one rank's candidate block: value plane then index plane, 8-byte entries (4*B*k words)
+  size_t ctrl_offset;    // words from the allocation's start to the control words
   size_t send_offset;    // words from the allocation's start to the send block
   size_t total_bytes;
   uint32_t* base;        // this rank's allocation
@@ -478,9 +473,9 @@ int ff_cp_exchange_create(int32_t world, int32_t rank, int32_t B, int32_t k, voi
   ex->B = B;
   ex->k = k;
   ex->device = device;
-  ex->slot_words = (2 * static_cast<size_t>(B) * k + 3) & ~static_cast<size_t>(3);
-  ex->flag_offset = 2 * static_cast<size_t>(world) * ex->slot_words;
-  ex->send_offset = ex->flag_offset + 64;   // 2 * kMaxPeers flags + the step counter, padded to 256 bytes
+  ex->slot_words = 4 * static_cast<size_t>(B) * k;
+  ex->ctrl_offset = 2 * static_cast<size_t>(world) * ex->slot_words;
+  ex->send_offset = ex->ctrl_offset + ff::kCtrlWords;
   ex->total_bytes = (ex->send_offset + ex->slot_words) * sizeof(uint32_t);
   for (int i = 0; i < ff::kMaxPeers; ++i) {
     ex->peer[i] = nullptr;
@@ -551,9 +546,24 @@ int ff_cp_exchange_destroy(void* handle) {
   return 0;
 }
 
-int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
-                    int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
-                    int32_t* status, void* stream) {
+}  // extern "C"
+
+namespace {
+
+// Whether a context-parallel step may run as ONE kernel (select, announce, wait, merge).
+// -1: decide from the launch shape; 0 / 1: forced by FF_TOPK_CP_FUSED (1 still needs a
+// launch whose CTAs are all resident at once).
+int cp_fused_setting() {
+  const char* env = getenv("FF_TOPK_CP_FUSED");
+  return env != nullptr ? atoi(env) : -1;
+}
+
+// fused_out == nullptr: send only (the merge is a later launch).  Otherwise the launch
+// merges too, if all its CTAs fit on the device together; *did_fuse tells.
+int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                 int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                 int32_t* status, void* stream, int32_t* fused_out, bool* did_fuse) {
+  if (did_fuse != nullptr) *did_fuse = false;
   if (handle == nullptr) return fail(FF_ERR_NULL, "exchange handle must not be NULL");
   FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
   for (int p = 0; p < ex->world; ++p)
@@ -585,13 +595,34 @@ int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const
   p.push_world = ex->world;
   p.push_rank = ex->rank;
   p.push_slot_words = static_cast<int64_t>(ex->slot_words);
-  p.push_flag_offset = static_cast<int64_t>(ex->flag_offset);
+  p.push_ctrl_offset = static_cast<int64_t>(ex->ctrl_offset);
   int cluster = choose_cluster(device, ex->B, L_width, ex->k);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     p.groups = choose_groups(device, ex->B, L_width, workspace_bytes, &cluster);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
+  if (fused_out != nullptr && cp_fused_setting() != 0) {
+    int log2c = 0;
+    while ((1 << log2c) < cluster) ++log2c;
+    const int64_t clusters = static_cast<int64_t>(ex->B) * (p.groups > 1 ? p.groups : 1);
+    if (log2c < 5 && clusters <= g_active_clusters[device][log2c]) {
+      p.push_fused = 1;
+      p.out_idx = fused_out;
+      if (did_fuse != nullptr) *did_fuse = true;
+    }
+  }
   return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                    int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream) {
+  return cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, workspace, workspace_bytes,
+                      status, stream, nullptr, nullptr);
 }
 
 int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx, int32_t* status,
@@ -600,9 +631,9 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
   FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
   ff::CpMergeParams p = {};
   p.recv_even = ex->base;
-  p.parity_stride = static_cast<int64_t>(ex->world) * static_cast<int64_t>(ex->slot_words);
+  p.parity_words = static_cast<int64_t>(ex->world) * static_cast<int64_t>(ex->slot_words);
   p.slot_words = static_cast<int64_t>(ex->slot_words);
-  p.flags = ex->base + ex->flag_offset;
+  p.ctrl = ex->base + ex->ctrl_offset;
   p.lengths = lengths;
   p.out_idx = out_idx;
   p.status = status;
@@ -622,9 +653,11 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
 int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
                     int32_t* out_idx, int64_t L_width, int64_t shard_offset, void* workspace,
                     size_t workspace_bytes, int32_t* status, void* stream) {
-  const int rc = ff_topk_cp_send(handle, scores, row_stride, lengths, L_width, shard_offset, workspace,
-                                 workspace_bytes, status, stream);
-  if (rc != 0) return rc;
+  if (out_idx == nullptr) return fail(FF_ERR_NULL, "out_idx must not be NULL");
+  bool fused = false;
+  const int rc = cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, workspace,
+                              workspace_bytes, status, stream, out_idx, &fused);
+  if (rc != 0 || fused) return rc;
   return ff_topk_cp_recv_merge(handle, lengths, out_idx, status, stream);
 }
 

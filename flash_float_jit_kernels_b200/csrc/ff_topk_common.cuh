@@ -84,14 +84,12 @@ struct TopkParams {
   int32_t* status;             // optional soft-error word
   int32_t groups;              // clusters per row (> 1 needs workspace and a cooperative launch)
   uint32_t* workspace;         // zero-filled global scratch, kWsRowWords words per row
-  const uint32_t* wait_flags;  // merge mode: [2][16] flags raised by the peers' pushes, step counter after them; or null
-  int32_t wait_n;              // number of peers
-  int64_t parity_stride;       // elements between the receive buffers of even and odd steps
   PeerPtrs push_peers;         // context-parallel send: results go to these exchange buffers
   int32_t push_world;          // > 0 switches the push on
   int32_t push_rank;
   int64_t push_slot_words;
-  int64_t push_flag_offset;
+  int64_t push_ctrl_offset;    // words from an exchange buffer's start to its control words
+  int32_t push_fused;          // 1: the same launch also waits for the peers and merges (single-kernel step)
   unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
 

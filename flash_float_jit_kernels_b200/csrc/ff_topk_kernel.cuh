@@ -790,17 +790,24 @@ __device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C
 // Writes output slot j of `row` from a window-relative index (or -1) and key.
 // In push mode (context-parallel send) the slot is not written locally at all: the (value,
 // global index) pair goes straight into this rank's slot of every peer's receive buffer.
-__device__ __forceinline__ void emit(const TopkParams& p, int64_t push_off, int row, int j, int32_t idx,
+// Context-parallel send: the step of this launch and where its entries go in a peer's buffer.
+struct PushCtx {
+  int64_t off;     // words from a peer's base to this rank's slot of this step's parity
+  uint32_t step;
+};
+
+__device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, int row, int j, int32_t idx,
                                      uint32_t key, bool is_map, int table_row) {
   if (p.push_world > 0) {
-    const uint32_t vbits = idx < 0 ? 0xff800000u : bits_of_key(key);
+    // one self-validating 8-byte entry per plane and peer: {payload, step}
+    const uint32_t vbits = idx < 0 ? kNoCandidateBits : bits_of_key(key);
     const uint32_t gidx = idx < 0 ? 0xffffffffu : static_cast<uint32_t>(idx + p.shard_offset);
-    const size_t at = static_cast<size_t>(row) * p.k + j;
-    const size_t plane = static_cast<size_t>(p.B) * p.k;
+    const size_t at = 2 * (static_cast<size_t>(row) * p.k + j);
+    const size_t plane = 2 * static_cast<size_t>(p.B) * p.k;
     for (int q = 0; q < p.push_world; ++q) {
-      uint32_t* slot = p.push_peers.base[q] + push_off;
-      slot[at] = vbits;
-      slot[plane + at] = gidx;
+      uint32_t* slot = p.push_peers.base[q] + push.off;
+      st_entry(slot + at, vbits, push.step);
+      st_entry(slot + plane + at, gidx, push.step);
     }
     return;
   }
@@ -830,7 +837,7 @@ __device__ __forceinline__ float prefilter_value(uint32_t key_lo) {
 
 template <bool HAS_MAP>
 __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
-                                              int64_t push_off) {
+                                              const PushCtx& push) {
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
   uint32_t* merged = reinterpret_cast<uint32_t*>(smem + kSmemStage);
@@ -849,17 +856,6 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const int tid = threadIdx.x;
   const int k = p.k;
 
-  // ---- context-parallel merge: the candidates are only valid once every peer has pushed ----
-  int64_t recv_shift = 0;   // elements from the even-step receive buffer to the one of this step
-  if (HAS_MAP && p.wait_flags != nullptr) {
-    const uint32_t step = p.wait_flags[kEpochWord];   // written by this step's push kernel (earlier launch)
-    const int parity = static_cast<int>(step & 1u);
-    recv_shift = parity * p.parity_stride;
-    if (!wait_for_peers(p.wait_flags + parity * kMaxPeers, p.wait_n, step) && p.status != nullptr &&
-        threadIdx.x == 0)
-      atomicOr(p.status, 2);
-  }
-
   // ---- row geometry (uniform over the cluster) ---------------------------
   const int rs = p.row_starts != nullptr ? p.row_starts[row] : 0;
   const int glen = p.lengths != nullptr ? p.lengths[row] : 0;
@@ -873,9 +869,9 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (l < 0) l = 0;
     len = static_cast<int>(l);
   }
-  const float* rowp = p.scores + static_cast<int64_t>(row) * p.row_stride + rs + recv_shift;
+  const float* rowp = p.scores + static_cast<int64_t>(row) * p.row_stride + rs;
   const int32_t* imap =
-      HAS_MAP ? p.idx_map + static_cast<int64_t>(row) * p.row_stride + rs + recv_shift : nullptr;
+      HAS_MAP ? p.idx_map + static_cast<int64_t>(row) * p.row_stride + rs : nullptr;
 
   int table_row = row;
   if (p.epilogue == 1 && p.cu_seqlens_q != nullptr) {
@@ -899,13 +895,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       __syncthreads();
       for (int j = tid; j < k; j += kThreads) {
         if (j >= len) {
-          emit(p, push_off, row, j, -1, 0u, false, table_row);
+          emit(p, push, row, j, -1, 0u, false, table_row);
           continue;
         }
         const uint64_t c = stage[j];
         int pos = 0;
         for (int q = 0; q < len; ++q) pos += stage[q] > c ? 1 : 0;
-        emit(p, push_off, row, pos, comp_index(c), comp_key(c), false, table_row);
+        emit(p, push, row, pos, comp_index(c), comp_key(c), false, table_row);
       }
       return;
     }
@@ -914,13 +910,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         // no more candidates than k slots: pass them through in position order
         const int64_t a = j < len ? seg_addr(j, p.seg_len, p.seg_stride) : 0;
         const int32_t idx = j < len ? imap[a] : -1;
-        emit(p, push_off, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
+        emit(p, push, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
       } else {
         const int n = HAS_MAP ? glen : len;
         const bool v = j < n;
         uint32_t key = 0u;
         if (v && !HAS_MAP && p.out_val != nullptr) key = key_of(rowp[j]);
-        emit(p, push_off, row, j, v ? j : -1, key, HAS_MAP, table_row);
+        emit(p, push, row, j, v ? j : -1, key, HAS_MAP, table_row);
       }
     }
     return;
@@ -1187,7 +1183,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   if (!ok) {
     if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
     if (my_share == 0) {
-      for (int j = tid; j < k; j += kThreads) emit(p, push_off, row, j, -1, 0u, HAS_MAP, table_row);
+      for (int j = tid; j < k; j += kThreads) emit(p, push, row, j, -1, 0u, HAS_MAP, table_row);
     }
     return;
   }
@@ -1357,7 +1353,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
-    if (pos < k) emit(p, push_off, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (pos < k) emit(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
   }
   FF_TRACE(p, 25);
 }
@@ -1368,36 +1364,61 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   __shared__ ClusterShared sh;
   // Context-parallel send: this launch also delivers its result to the peers.  The step number is
   // read from device memory (graph replays), the slot it selects is fixed for the whole launch.
-  uint32_t step = 0;
-  int64_t push_off = 0;
-  uint32_t* mine = nullptr;
+  PushCtx push;
+  push.off = 0;
+  push.step = 0u;
+  uint32_t* ctrl = nullptr;
   if (!HAS_MAP && p.push_world > 0) {
-    mine = p.push_peers.base[p.push_rank] + p.push_flag_offset;
-    step = *reinterpret_cast<volatile uint32_t*>(mine + kEpochWord) + 1u;
-    push_off = (static_cast<int64_t>(step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
+    ctrl = p.push_peers.base[p.push_rank] + p.push_ctrl_offset;
+    push.step = *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) + 1u;
+    push.off = (static_cast<int64_t>(push.step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
   }
-  topk_row_body<HAS_MAP>(p, smem, sh, push_off);
+  topk_row_body<HAS_MAP>(p, smem, sh, push);
   if (!HAS_MAP && p.push_world > 0) {
-    // Every thread publishes its remote stores; the CTA that finishes last in the whole launch
-    // raises this rank's flag in every peer and advances the step counter.
-    __syncthreads();
-    bool last = false;
-    if (threadIdx.x == 0) {
-      __threadfence();          // device scope: cumulative over the CTA's stores ordered before the barrier
-      last = atomicAdd(mine + kPushDoneWord, 1u) == gridDim.x - 1u;
-    }
-    if (last) {
-      // the release chain of every CTA ends here; one system-scope fence covers all their stores
-      __threadfence_system();
-      const int parity = static_cast<int>(step & 1u);
-      for (int q = 0; q < p.push_world; ++q) {
-        uint32_t* flag = p.push_peers.base[q] + p.push_flag_offset + static_cast<size_t>(parity) * kMaxPeers +
-                         p.push_rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+    // Every CTA read the step long ago; the one that counts itself last advances the counter.
+    // A thread outside warp 0 does it, so that its round trip overlaps the merge below.
+    if (threadIdx.x == 32) {
+      if (atomicAdd(ctrl + kPushDoneWord, 1u) == gridDim.x - 1u) {
+        ctrl[kPushDoneWord] = 0u;
+        __threadfence();
+        *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) = push.step;
       }
-      mine[kPushDoneWord] = 0u;
-      __threadfence();
-      *reinterpret_cast<volatile uint32_t*>(mine + kEpochWord) = step;
+    }
+    if (p.push_fused != 0) {
+      // Single-kernel step: merge this row's world x k candidates right here.  The row's CTAs
+      // share them out (at least one per thread); each stages all run keys in shared memory,
+      // polling every entry until it carries this step, and ranks its share by binary searches.
+      // All CTAs of the launch are resident at once (checked by the host), so a CTA that polls
+      // cannot keep a CTA that has yet to store its entries from running.
+      cg::cluster_group cluster = cg::this_cluster();
+      const int C = static_cast<int>(cluster.num_blocks());
+      const int G = max(p.groups, 1);
+      const int row = static_cast<int>(blockIdx.x) / (C * G);
+      const int n_share = C * G;
+      const int my_share = (static_cast<int>(blockIdx.x) / C) % G * C + static_cast<int>(cluster.block_rank());
+      const int k = p.k;
+      const int world = p.push_world;
+      const int glen = p.lengths[row];
+      const int n_cand = world * k;
+      int per = (n_cand + n_share - 1) / n_share;
+      if (per < kThreads) per = kThreads;
+      const int begin = my_share * per;
+      int32_t* out_row = p.out_idx + static_cast<int64_t>(row) * k;
+      if (glen <= k) {   // short row: identity order, as everywhere else
+        if (my_share == 0)
+          for (int j = threadIdx.x; j < k; j += kThreads) out_row[j] = j < glen ? j : -1;
+      } else if (begin < n_cand) {
+        RunSource src;
+        src.base = p.push_peers.base[p.push_rank] + static_cast<int64_t>(push.step & 1u) * world * p.push_slot_words;
+        src.slot_words = p.push_slot_words;
+        src.plane_words = 2 * static_cast<int64_t>(p.B) * k;
+        src.row_words = 2 * static_cast<int64_t>(row) * k;
+        uint32_t* run_keys = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [world][k], at most 128 KiB
+        __syncthreads();   // the ring region is free in the whole CTA
+        bool ok = stage_run_keys(src, world, k, push.step, run_keys);
+        ok = rank_and_write(src, run_keys, world, k, push.step, begin, min(n_cand, begin + per), out_row) && ok;
+        if (!ok && p.status != nullptr) atomicOr(p.status, 2);
+      }
     }
   }
 }

@@ -187,3 +187,73 @@ def test_peer_exchange_with_shards_shorter_than_k(oracle):
         torch.cuda.synchronize()
         for h in exs:
             lib.ff_cp_exchange_destroy(h)
+
+
+def test_single_kernel_step_on_one_rank(oracle):
+    """world == 1: ff_topk_cp_step runs select, announcement, wait and merge as ONE launch (the
+    kernel waits only for its own CTAs, all resident).  Several steps over both receive buffers,
+    rows split over clusters and not, ragged and short rows, and a two-kernel step in between."""
+    import ctypes
+    from flash_float_jit_kernels_b200 import _lib
+    from flash_float_jit_kernels_b200.topk_indexer import _ptr, _workspace
+    lib = _lib.load()
+    lib.ff_topk_set_cluster_override(0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    for (B, L, k) in ((1, 1 << 20, 2048), (3, 70000, 512)):
+        h = ctypes.c_void_p()
+        assert lib.ff_cp_exchange_create(1, 0, B, k, ctypes.byref(h)) == 0
+        try:
+            ws, ws_bytes = _workspace(lib, dev, B, L, k)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            out = torch.empty((B, k), dtype=torch.int32, device=dev)
+            for step in range(5):
+                s = torch.randn((B, L), generator=torch.Generator().manual_seed(700 + step)).to(torch.bfloat16).float()
+                lengths = torch.full((B,), L - 17 * step, dtype=torch.int32)
+                if B > 1:
+                    lengths[1] = 300 + step          # <= k: identity order
+                    lengths[2] = 20000 + 1000 * step
+                sd, ld = s.to(dev), lengths.to(dev)
+                launches = lib.ff_topk_launch_count()
+                if step == 2:                        # the two-kernel form on the same exchange
+                    assert lib.ff_topk_cp_send(h, sd.data_ptr(), sd.stride(0), ld.data_ptr(), L, 0, _ptr(ws),
+                                               ws_bytes, status.data_ptr(), stream) == 0
+                    assert lib.ff_topk_cp_recv_merge(h, ld.data_ptr(), out.data_ptr(), status.data_ptr(), stream) == 0
+                    assert lib.ff_topk_launch_count() - launches == 2
+                else:
+                    assert lib.ff_topk_cp_step(h, sd.data_ptr(), sd.stride(0), ld.data_ptr(), out.data_ptr(), L, 0,
+                                               _ptr(ws), ws_bytes, status.data_ptr(), stream) == 0
+                    assert lib.ff_topk_launch_count() - launches == 1, "the step should be a single launch"
+                torch.cuda.synchronize()
+                assert int(status.item()) == 0
+                assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), (B, step)
+        finally:
+            torch.cuda.synchronize()
+            lib.ff_cp_exchange_destroy(h)
+
+
+def test_single_kernel_step_with_a_missing_peer_times_out():
+    """Rank 1 never runs: rank 0's single-kernel step gives up after its one-second bounded wait,
+    reports FF_STATUS_WAIT_TIMEOUT, and the context stays usable."""
+    from flash_float_jit_kernels_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    B, L, k = 1, 50000, 256
+    exs = _make_exchanges(lib, 2, B, k)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        s = torch.randn((B, L), device=dev)
+        lengths = torch.tensor([2 * L], dtype=torch.int32, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        out = torch.empty((B, k), dtype=torch.int32, device=dev)
+        launches = lib.ff_topk_launch_count()
+        assert lib.ff_topk_cp_step(exs[0], s.data_ptr(), s.stride(0), lengths.data_ptr(), out.data_ptr(), L, 0,
+                                   None, 0, status.data_ptr(), stream) == 0
+        assert lib.ff_topk_launch_count() - launches == 1
+        torch.cuda.synchronize()
+        assert int(status.item()) & 2, "the wait for the absent peer should have timed out"
+        assert float(torch.ones(4, device=dev).sum()) == 4.0           # context still usable
+    finally:
+        torch.cuda.synchronize()
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
