@@ -396,7 +396,7 @@ def bench_cp(args):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
-    # With the peer-memory exchange a step is three kernel launches and no library call, so the
+    # With the peer-memory exchange a step is one kernel launch and no library call, so the
     # K steps are captured into one CUDA graph (the step counter lives in device memory);
     # with the NCCL exchange they are launched eagerly.
     graph = None
@@ -491,13 +491,14 @@ def bench_cp(args):
                        "l2": f"each rank rotates over {n_rot} distinct 4 MiB shards (128 MiB > 126 MB L2)",
                        "timing": ("K steps in one CUDA graph replay" if graph is not None else
                                   "eager stream launches") + ", CUDA events, max over ranks",
-                       "exchange": ("stores into every peer's receive buffer over NVLink + flags (16 KiB per "
-                                    "rank per peer), merge waits on local flags" if plan.exchange == "p2p" else
+                       "exchange": ("self-validating 8-byte entries stored into every peer's receive buffer "
+                                    "over NVLink from the select kernel (32 KiB per rank per peer); the same "
+                                    "launch polls its local entries and merges" if plan.exchange == "p2p" else
                                     "NCCL all-gather of (value, global index) candidates, 16 KiB per rank")},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak * world, "unit": "GB/s",
                          "frac": round(achieved / (peak * world), 5), "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": algo_bytes,
-                         "note": "whole step (select + all-gather + merge) against N x the HBM peak"},
+                         "note": "whole step (select + exchange + merge) against N x the HBM peak"},
             "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": 4 * L_SHARD,
                     "d2h_bytes_per_step": 4 * k, "steps": Ke},
             "gpu_launches": int(launches),
