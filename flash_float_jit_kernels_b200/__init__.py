@@ -9,6 +9,7 @@ from .topk_indexer import (  # noqa: F401
     fast_topk_v3,
     fast_topk_transform_fused,
     fast_topk_transform_ragged_fused,
+    new_threshold_hint,
 )
 from .context_parallel import fast_topk_v3_cp, shard_bounds  # noqa: F401
 
@@ -17,6 +18,7 @@ __all__ = [
     "fast_topk_v3",
     "fast_topk_transform_fused",
     "fast_topk_transform_ragged_fused",
+    "new_threshold_hint",
     "fast_topk_v3_cp",
     "shard_bounds",
 ]

@@ -32,6 +32,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p],
     ),
+    "ff_topk_launch_hinted": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32,
+         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     "ff_topk_transform_launch": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_int32,
@@ -70,6 +75,7 @@ FF_EPILOGUE_INDEX = 0
 FF_EPILOGUE_PAGE_TABLE = 1
 FF_EPILOGUE_ADD_OFFSET = 2
 FF_TOPK_MAX_K = 2048
+FF_STATUS_HINT_MISSED = 8
 
 
 class LibraryMissingError(RuntimeError):

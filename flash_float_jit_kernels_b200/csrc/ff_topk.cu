@@ -275,12 +275,17 @@ int ff_topk_set_groups_override(int32_t g) {
   return 0;
 }
 
-int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
-                             const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
-                             int32_t k, int32_t epilogue, const int32_t* table,
-                             int64_t table_stride, const int32_t* cu_seqlens_q,
-                             int32_t n_table_rows, const int32_t* offsets, void* workspace,
-                             size_t workspace_bytes, int32_t* status, void* stream) {
+}  // extern "C"
+
+namespace {
+
+int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
+                          int32_t k, int32_t epilogue, const int32_t* table,
+                          int64_t table_stride, const int32_t* cu_seqlens_q,
+                          int32_t n_table_rows, const int32_t* offsets, const float* hint_in,
+                          float* hint_out, void* workspace, size_t workspace_bytes, int32_t* status,
+                          void* stream) {
   int rc = check_common(B, L_width, k);
   if (rc != 0) return rc;
   if (B == 0) return 0;
@@ -318,12 +323,38 @@ int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int3
   p.n_table_rows = n_table_rows;
   p.offsets = offsets;
   p.status = status;
+  p.hint_in = hint_in;
+  p.hint_out = hint_out;
   int cluster = choose_cluster(device, B, L_width, k);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
   return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
+                             const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
+                             int32_t k, int32_t epilogue, const int32_t* table,
+                             int64_t table_stride, const int32_t* cu_seqlens_q,
+                             int32_t n_table_rows, const int32_t* offsets, void* workspace,
+                             size_t workspace_bytes, int32_t* status, void* stream) {
+  return transform_launch_impl(scores, row_stride, lengths, row_starts, out, B, L_width, k, epilogue, table,
+                               table_stride, cu_seqlens_q, n_table_rows, offsets, nullptr, nullptr, workspace,
+                               workspace_bytes, status, stream);
+}
+
+int ff_topk_launch_hinted(const float* scores, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                          int32_t k, const float* hint_in, float* hint_out, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream) {
+  return transform_launch_impl(scores, row_stride, lengths, row_starts, out_idx, B, L_width, k,
+                               FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, hint_in, hint_out, workspace,
+                               workspace_bytes, status, stream);
 }
 
 int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengths,

@@ -82,6 +82,8 @@ struct TopkParams {
   int32_t n_table_rows;
   const int32_t* offsets;      // [B] ragged offsets
   int32_t* status;             // optional soft-error word
+  const float* hint_in;        // [B] or null: a guess of a value between each row's k-th and 4096-th largest (NaN: none)
+  float* hint_out;             // [B] or null: receives such a value for this call's rows (may alias hint_in)
   int32_t groups;              // clusters per row (> 1 needs workspace and a cooperative launch)
   uint32_t* workspace;         // zero-filled global scratch, kWsRowWords words per row
   PeerPtrs push_peers;         // context-parallel send: results go to these exchange buffers

@@ -481,6 +481,7 @@ __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_un
 //   [0, 6)   arrivals at the histogram barrier of digit level 0..5
 //   [6]      arrivals at the survivor barrier      [7] CTAs that are done
 //   [8]      survivors appended so far
+//   [9]      arrivals at the barrier of a hinted attempt   [10] survivors it appended
 //   [64, 320) first digit level only: the row's histogram summed in groups of 32 bins
 //   [320, 320 + 6 * 8192)        one 8192-bin global histogram per digit level
 //   [320 + 6 * 8192, + 2 * 4096) survivor list (4096 x 64-bit composites)
@@ -888,6 +889,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
   if (identity || len <= k) {
     if (my_share != 0) return;
+    if (!HAS_MAP && p.hint_out != nullptr && tid == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);   // no guess
     if (!HAS_MAP && p.out_val != nullptr) {
       // Context-parallel shard shorter than k: every position is a candidate, but the
       // merge expects the run in canonical order, so rank the few elements by counting.
@@ -925,8 +927,6 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const Chunk chunk = make_chunk(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
 
-  // ---- level 0: 13-bit histogram of the whole chunk -----------------------
-  for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
   TileStream ts;
   ts.src = reinterpret_cast<const float4*>(chunk.abase) + chunk.fb;
   ts.ring = smem_addr(smem + kSmemRing);
@@ -948,6 +948,119 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
   }
+
+  int r = k;                // survivors still to be taken from the current candidate set
+  uint64_t P = 0;           // digits fixed so far (value of comp >> shift of the last level)
+  bool src_is_cand = false; // candidates live in `cand` instead of the chunk
+  int cand_n = 0;
+  bool ok = true;
+  int expected_total = 0;
+  int levels_used = 0;
+  uint64_t floor_comp = 0;  // no survivor's composite is below this
+
+  // Stores this CTA's n_true staged survivors (the first kSortCap of them are in `stage`)
+  // where every CTA working on the row will find them: one atomic reserves a block of slots
+  // (the same in every copy of the list), coalesced stores fill it.  Inside one cluster the
+  // list is all-gathered into EVERY peer over DSMEM, so each CTA ends up with the full list and
+  // can take a share of the finishing work without further exchange; rows split over clusters
+  // keep it in global scratch (count word `gcount`).
+  auto gather_stage = [&](int n_true, uint32_t* gcount) {
+    const int n_stage = min(n_true, kSortCap);
+    if (n_true > 0 && G > 1) {
+      if (tid == 0) sh.push_base = static_cast<int>(atomicAdd(gcount, static_cast<uint32_t>(n_true)));
+      __syncthreads();
+      uint64_t* gsurv = reinterpret_cast<uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+      const int base = sh.push_base;
+      for (int i = tid; i < n_stage; i += kThreads) {
+        if (base + i < kSortCap) gsurv[base + i] = stage[i];
+      }
+    } else if (n_true > 0) {
+      if (C == 1) {
+        const int base = sh.sort_count;
+        __syncthreads();
+        for (int i = tid; i < n_stage; i += kThreads) {
+          if (base + i < kSortCap) sortbuf[base + i] = stage[i];
+        }
+        if (tid == 0) sh.sort_count = base + n_true;
+      } else {
+        if (tid == 0) {
+          sh.push_base = static_cast<int>(dsmem_atomic_add_u32(
+              dsmem_addr(smem_addr(&sh.sort_count), 0), static_cast<uint32_t>(n_true)));
+        }
+        __syncthreads();
+        const int base = sh.push_base;
+        const uint32_t sort_local = smem_addr(sortbuf);
+        for (int j = tid; j < n_stage * C; j += kThreads) {
+          const int c = j / n_stage;
+          const int i = j - c * n_stage;
+          if (base + i < kSortCap)
+            dsmem_st_u64(dsmem_addr(sort_local + 8u * static_cast<uint32_t>(base + i), c), stage[i]);
+        }
+      }
+    }
+    __syncthreads();
+  };
+
+  // ---- hinted attempt: one sweep, no histogram ------------------------------
+  // The caller's guess h of a value between the row's k-th and 4096-th largest: everything
+  // not below h is collected in one sweep; if that is between k and 4096 elements the row is
+  // finished from them directly.  Otherwise (a miss, reported as FF_STATUS_HINT_MISSED) the
+  // row starts over on the histogram path below; the result is exact either way.
+  bool hinted_done = false;
+  float hint = 0.f;
+  bool use_hint = false;
+  if (!HAS_MAP && p.hint_in != nullptr) {
+    hint = p.hint_in[row];
+    use_hint = hint == hint;   // NaN: no guess
+  }
+  __syncthreads();
+  if (use_hint) {
+    stream_pass(ts, [&](uint32_t tile, int tt, int units) {
+      collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, hint, stage, kSortCap, &sh.stage_count);
+    });
+    {
+      float x = 0.f;
+      const int pos = partial_element(chunk, x);
+      if (pos >= 0 && !(x < hint)) {
+        const int slot = atomicAdd(&sh.stage_count, 1);
+        if (slot < kSortCap) stage[slot] = make_comp(key_of(x), pos);
+      }
+    }
+    __syncthreads();
+    FF_TRACE(p, 3);
+    gather_stage(sh.stage_count, G > 1 ? ws + 10 : nullptr);
+    FF_TRACE(p, 4);
+    int total;
+    if (G > 1) {
+      if (!row_barrier(ws + 9, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
+      total = static_cast<int>(__ldcg(ws + 10));
+    } else if (C > 1) {
+      cluster.sync();
+      total = static_cast<int>(dsmem_ld_u32(dsmem_addr(smem_addr(&sh.sort_count), 0)));
+    } else {
+      total = sh.sort_count;
+    }
+    if (total >= k && total <= kSortCap) {
+      hinted_done = true;
+      expected_total = total;
+      floor_comp = static_cast<uint64_t>(key_of(hint)) << 32;
+      if (G > 1) {
+        const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+        for (int i = tid; i < total; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
+        if (my_share == 0 && tid == 0) sh.sort_count = total;
+      }
+    } else {
+      if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 8);
+      if (C > 1 && G == 1) cluster.sync();   // every CTA has read the count before it is cleared
+      if (tid == 0) sh.sort_count = 0;
+    }
+    if (tid == 0) sh.stage_count = 0;
+    __syncthreads();
+  }
+
+  if (!hinted_done) {
+  // ---- level 0: 13-bit histogram of the whole chunk -----------------------
+  for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
   __syncthreads();
   if (HAS_MAP) {
     for_each_in_chunk<true>(
@@ -972,15 +1085,6 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   }
   __syncthreads();
   FF_TRACE(p, 1);
-
-  int r = k;                // survivors still to be taken from the current candidate set
-  uint64_t P = 0;           // digits fixed so far (value of comp >> shift of the last level)
-  bool src_is_cand = false; // candidates live in `cand` instead of the chunk
-  int cand_n = 0;
-  bool ok = true;
-  int expected_total = 0;
-  int levels_used = 0;
-  uint64_t floor_comp = 0;  // no survivor's composite is below this
 
 #pragma unroll 1
   for (int level = 0; level < kNumLevels; ++level) {
@@ -1102,45 +1206,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     __syncthreads();
     FF_TRACE(p, 3 + 3 * level);
 
-    // All-gather this CTA's survivors into EVERY peer's survivor list: one remote
-    // atomic on rank 0 reserves a block of slots (the same in every copy), then
-    // coalesced remote stores fill it.  Each CTA ends up with the full list and
-    // can take a share of the finishing work without further exchange.
-    const int n_stage = min(sh.stage_count, kSortCap);
-    if (n_stage > 0 && G > 1) {
-      // rows split over clusters: the survivor list lives in global scratch
-      if (tid == 0) sh.push_base = static_cast<int>(atomicAdd(ws + 8, static_cast<uint32_t>(n_stage)));
-      __syncthreads();
-      uint64_t* gsurv = reinterpret_cast<uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
-      const int base = sh.push_base;
-      for (int i = tid; i < n_stage; i += kThreads) {
-        if (base + i < kSortCap) gsurv[base + i] = stage[i];
-      }
-    } else if (n_stage > 0) {
-      if (C == 1) {
-        const int base = sh.sort_count;
-        __syncthreads();
-        for (int i = tid; i < n_stage; i += kThreads) {
-          if (base + i < kSortCap) sortbuf[base + i] = stage[i];
-        }
-        if (tid == 0) sh.sort_count = base + n_stage;
-      } else {
-        if (tid == 0) {
-          sh.push_base = static_cast<int>(dsmem_atomic_add_u32(
-              dsmem_addr(smem_addr(&sh.sort_count), 0), static_cast<uint32_t>(n_stage)));
-        }
-        __syncthreads();
-        const int base = sh.push_base;
-        const uint32_t sort_local = smem_addr(sortbuf);
-        for (int j = tid; j < n_stage * C; j += kThreads) {
-          const int c = j / n_stage;
-          const int i = j - c * n_stage;
-          if (base + i < kSortCap)
-            dsmem_st_u64(dsmem_addr(sort_local + 8u * static_cast<uint32_t>(base + i), c), stage[i]);
-        }
-      }
-    }
-    __syncthreads();
+    gather_stage(min(sh.stage_count, kSortCap), G > 1 ? ws + 8 : nullptr);
     FF_TRACE(p, 4 + 3 * level);
     if (tid == 0) sh.stage_count = 0;
     if (ctx.compact && !src_is_cand) {
@@ -1155,13 +1221,16 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     r -= above;
     P = Pn;
   }
+  }   // !hinted_done
 
   if (G > 1) {
-    if (!row_barrier(ws + 6, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
-    const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
-    const int n_load = ok ? min(expected_total, kSortCap) : 0;
-    for (int i = tid; i < n_load; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
-    if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));
+    if (!hinted_done) {
+      if (!row_barrier(ws + 6, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
+      const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+      const int n_load = ok ? min(expected_total, kSortCap) : 0;
+      for (int i = tid; i < n_load; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
+      if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));
+    }
     __syncthreads();
     // Last use of the scratch: the CTA that counts in last zeroes it for the next launch.
     if (tid == 0) {
@@ -1173,7 +1242,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       for (int i = tid; i < kWsHeaderWords + levels_used * kMaxBins; i += kThreads) ws[i] = 0u;
     }
   } else if (C > 1) {
-    cluster.sync();   // every survivor has landed in every CTA's list
+    if (!hinted_done) cluster.sync();   // every survivor has landed in every CTA's list
   } else {
     __syncthreads();
   }
@@ -1182,12 +1251,14 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   if (ts.timed_out && p.status != nullptr && tid == 0) atomicOr(p.status, 2);
   if (!ok) {
     if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
+    if (!HAS_MAP && p.hint_out != nullptr && tid == 0 && my_share == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);
     if (my_share == 0) {
       for (int j = tid; j < k; j += kThreads) emit(p, push, row, j, -1, 0u, HAS_MAP, table_row);
     }
     return;
   }
   const int T = min(expected_total, kSortCap);
+  const int hint_rank = min(T, k + (k >> 1)) - 1;
   if (my_share == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
     atomicOr(p.status, 1);
 
@@ -1354,6 +1425,36 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
     if (pos < k) emit(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+  }
+  // Next call's guess: a score of rank about 3k/2, so that about 3k/2 elements (between k and
+  // 4096) pass it on similar data.  With T >= 3k/2 survivors it is the lower edge of the bucket
+  // that holds that rank; with fewer it is extrapolated linearly below the smallest survivor
+  // from the ranks T/2 and T.  Two lanes of the row's first CTA each find one bucket by a
+  // binary search over the buckets' suffix counts (the same in every CTA).
+  if (!HAS_MAP && p.hint_out != nullptr && my_share == 0 && tid < 32) {
+    const int want = k + (k >> 1);
+    const int rank_a = min(T, want) - 1;
+    const int rank_m = T >> 1;
+    const int rank_mine = (tid & 1) ? rank_m : rank_a;
+    int b_lo = 0, b_hi = kFinishBins - 1;   // largest bucket b with #(bins >= b) > rank
+#pragma unroll 1
+    while (b_lo < b_hi) {
+      const int mid = (b_lo + b_hi + 1) >> 1;
+      const uint32_t pm = pad(static_cast<uint32_t>(mid));
+      if (static_cast<int>(E[pm] + fh[pm]) > rank_mine) b_lo = mid; else b_hi = mid - 1;
+    }
+    const uint64_t edge = lo + (static_cast<uint64_t>(b_lo) << bshift);
+    const float v_mine = __uint_as_float(bits_of_key(comp_key(edge)));
+    const float va = __shfl_sync(0xffffffffu, v_mine, 0);
+    const float vm = __shfl_sync(0xffffffffu, v_mine, 1);
+    if (tid == 0) {
+      float guess = va;
+      if (T < want && rank_a > rank_m) {
+        const float lower = va - (vm - va) * (static_cast<float>(want - 1 - rank_a) / static_cast<float>(rank_a - rank_m));
+        if (lower == lower && fabsf(lower) <= 3.0e38f) guess = lower;   // finite
+      }
+      p.hint_out[row] = guess;
+    }
   }
   FF_TRACE(p, 25);
 }

@@ -88,6 +88,7 @@ def fast_topk_v3(
     *,
     out: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
+    threshold_hint: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Top-k indices of every row of ``score`` (reference: ``topk_indexer.py:109``).
 
@@ -101,6 +102,15 @@ def fast_topk_v3(
         out: optional preallocated (B, topk) int32 result (extension; lets a
             caller keep the call allocation-free inside a CUDA graph).
         status: optional int32 device scalar that collects soft-error bits.
+        threshold_hint: optional (B) float32 device tensor, read AND updated
+            (extension; see :func:`new_threshold_hint`).  Entry ``i`` is a guess
+            of a score between row ``i``'s k-th and 4096-th largest, NaN for "no
+            guess".  A row with a fitting guess is swept once instead of twice
+            and skips the histogram exchange; a guess that does not fit costs one
+            extra sweep (``FF_STATUS_HINT_MISSED`` in ``status``).  The result
+            is the same exact top-k either way.  On return the entry holds a
+            score of rank about 1.5 k of this call's row: pass the tensor again
+            for the next call on similar rows (the next decode step).
 
     Returns:
         (B, topk) int32 indices in (value desc, index asc) order, ``-1``
@@ -117,13 +127,27 @@ def fast_topk_v3(
     if B == 0:
         return out
     ws, ws_bytes = _workspace(lib, score.device, B, L, topk)
+    row_stride = score.stride(0) if B > 1 else max(score.stride(0), L)
     with torch.cuda.device(score.device):
-        rc = lib.ff_topk_launch(
-            score.data_ptr(), score.stride(0) if B > 1 else max(score.stride(0), L),
-            lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
-            _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(score.device))
+        if threshold_hint is None:
+            rc = lib.ff_topk_launch(
+                score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
+                _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(score.device))
+        else:
+            _require(threshold_hint.shape == (B,) and threshold_hint.dtype == torch.float32
+                     and threshold_hint.is_contiguous() and threshold_hint.device == score.device,
+                     "threshold_hint must be a contiguous (B) float32 tensor on score's device")
+            rc = lib.ff_topk_launch_hinted(
+                score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
+                threshold_hint.data_ptr(), threshold_hint.data_ptr(), _ptr(ws), ws_bytes, _ptr(status),
+                _stream_ptr(score.device))
     _lib.check(rc, "fast_topk_v3")
     return out
+
+
+def new_threshold_hint(B: int, device) -> torch.Tensor:
+    """A (B) float32 tensor of NaN ("no guess yet") for ``fast_topk_v3(threshold_hint=...)``."""
+    return torch.full((B,), float("nan"), dtype=torch.float32, device=device)
 
 
 def fast_topk_transform_fused(

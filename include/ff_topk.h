@@ -43,6 +43,7 @@ extern "C" {
 #define FF_STATUS_COUNT_MISMATCH 1 /* gathered survivors != histogram count   */
 #define FF_STATUS_WAIT_TIMEOUT 2   /* a bounded cross-cluster wait ran out    */
 #define FF_STATUS_NO_THRESHOLD 4   /* no threshold digit found (corrupt hist) */
+#define FF_STATUS_HINT_MISSED 8    /* information, not an error: a threshold guess did not fit */
 
 /* Output epilogue applied to each selected window-relative index `p`
  * (reference: topk_indexer_radix.cu:1000-1124, the fused page-table
@@ -106,6 +107,23 @@ int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t
                           const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
                           int32_t k, int32_t* status, void* stream);
 
+/* ff_topk_launch with a threshold guess per row (no reference counterpart: the
+ * reference only discusses reusing the previous decode step's threshold,
+ * README.md:100-106).  hint_in[i] is a guess of a value between row i's k-th and
+ * 4096-th largest score (NaN = no guess for that row; hint_in may be NULL).  With
+ * a guess the row is swept ONCE: everything not below the guess is collected and,
+ * if that is between k and 4096 elements, ranked directly: no histogram, no merge
+ * of histograms, no second sweep.  If the guess does not fit, the row starts over
+ * on the normal path and FF_STATUS_HINT_MISSED is OR-ed into `status`; the result
+ * is exact and identical to ff_topk_launch's either way.  hint_out[i] (may be NULL,
+ * may alias hint_in) receives a score of rank about 1.5 k of row i (NaN for rows with
+ * no more than k positions): a good guess for the next call on similar data, e.g. the
+ * next decode step of the same sequences.  Device pointers, float32 [B]. */
+int ff_topk_launch_hinted(const float* scores, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
+                          int32_t k, const float* hint_in, float* hint_out, void* workspace,
+                          size_t workspace_bytes, int32_t* status, void* stream);
+
 /* Fused top-k + page-table gather / ragged offset.  Replaces
  * fast_topk_transform_fused and fast_topk_transform_ragged_fused
  * (topk_indexer_radix.cu:1549-1639).
@@ -148,17 +166,19 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
 
 /* ---- Context-parallel mode with the exchange fused over peer memory --------
  * (No reference counterpart.)  Instead of a collective library call, each rank
- * stores its candidates straight into every peer's receive buffer over NVLink
- * and raises a flag there; the merge kernel polls its own flags (bounded to one
- * second, FF_STATUS_WAIT_TIMEOUT on expiry) and reads local memory only.
+ * stores its candidates straight into every peer's receive buffer over NVLink as
+ * self-validating 8-byte entries {payload, step}; the merge polls its own (local)
+ * entries until they carry the current step (bounded to one second,
+ * FF_STATUS_WAIT_TIMEOUT on expiry).  No fence, flag or collective call.
  *
  *   ff_cp_exchange_create      allocates this rank's buffers (cudaMalloc) for a fixed (world, B, k)
  *   ff_cp_exchange_ipc_handle  64-byte cudaIpcMemHandle_t of that allocation, to be sent to the peers
  *   ff_cp_exchange_open_peers  maps the peers' allocations from `n` = world handles (rank-major, 64 B each)
  *   ff_cp_exchange_set_peer    in-process alternative: give peer p's base pointer directly
- *   ff_topk_cp_send            shard-local select + push to all peers (2 launches)
- *   ff_topk_cp_recv_merge      wait for all peers' pushes of the current step + merge (1 launch)
- *   ff_topk_cp_step            send followed by recv_merge
+ *   ff_topk_cp_send            shard-local select whose epilogue stores into all peers (1 launch)
+ *   ff_topk_cp_recv_merge      wait for all peers' entries of the current step + merge (1 launch)
+ *   ff_topk_cp_step            the whole step as ONE launch (select, store to peers, poll, merge) when
+ *                              all CTAs of the launch can be resident at once; else send + recv_merge
  * Every rank must call the step functions the same number of times in the same
  * order; a rank may run at most one step ahead of its peers (two alternating
  * receive buffers).  out_idx is [B, k] global indices, identical on all ranks. */

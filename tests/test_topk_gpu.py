@@ -298,3 +298,54 @@ def test_split_rows_deeper_levels_and_ties(ff, oracle, cluster, groups):
     rs = torch.tensor([0, 1, 2, 3], dtype=torch.int32)
     run_grouped(ff, oracle, s, lengths - 3, 2048, cluster, groups, rs)
     run_grouped(ff, oracle, s, lengths, 7, cluster, groups)
+
+
+@pytest.mark.parametrize("B,L,k", [(1, 1 << 20, 2048), (1, 300000, 1024), (4, 70000, 512), (64, 20000, 2048)])
+def test_threshold_hint_is_exact_hit_or_miss(oracle, B, L, k):
+    """A fitting guess takes the single-sweep path, a bad one falls back (status bit 8);
+    both give the oracle's result, and the returned guess fits the next similar row."""
+    from flash_float_jit_kernels_b200 import _lib, fast_topk_v3, new_threshold_hint
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(4242 + L)
+    lengths = torch.full((B,), L, dtype=torch.int32)
+    if B > 1:
+        lengths[1] = L - 4097
+        lengths[B - 1] = max(k + 5, L // 3)
+    hint = new_threshold_hint(B, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    missed = []
+    for step in range(4):
+        s = torch.randn((B, L), generator=g).to(torch.bfloat16).float()
+        out = fast_topk_v3(s.to(dev), lengths.to(dev), k, status=status, threshold_hint=hint)
+        torch.cuda.synchronize()
+        st = int(status.item()); status.zero_()
+        assert st & ~_lib.FF_STATUS_HINT_MISSED == 0
+        missed.append(bool(st & _lib.FF_STATUS_HINT_MISSED))
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), step
+        assert not torch.isnan(hint).any()
+    assert missed[0] is False           # no guess yet: nothing to miss
+    if B == 1:   # the status word is shared by the batch: one row's miss sets it
+        assert not all(missed[1:]), "guesses from the previous, similar row should mostly fit"
+    # guesses that cannot fit: far too high (fewer than k pass), far too low (more than 4096 pass)
+    for bad in (1e30, -1e30, float("inf"), float("-inf")):
+        hint.fill_(bad)
+        s = torch.randn((B, L), generator=g)
+        out = fast_topk_v3(s.to(dev), lengths.to(dev), k, status=status, threshold_hint=hint)
+        torch.cuda.synchronize()
+        assert int(status.item()) == _lib.FF_STATUS_HINT_MISSED; status.zero_()
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), bad
+
+
+def test_threshold_hint_short_rows_and_special_values(oracle):
+    from flash_float_jit_kernels_b200 import fast_topk_v3, new_threshold_hint
+    dev = torch.device("cuda:0")
+    B, L, k = 3, 9000, 512
+    s = torch.randn((B, L), generator=torch.Generator().manual_seed(77))
+    s[0, 100:200] = float("nan"); s[0, 300] = float("inf"); s[2, :] = 1.5       # NaN on top; an all-equal row
+    lengths = torch.tensor([L, 400, L], dtype=torch.int32)                     # row 1 is shorter than k
+    hint = new_threshold_hint(B, dev)
+    for step in range(3):
+        out = fast_topk_v3(s.to(dev), lengths.to(dev), k, threshold_hint=hint)
+        torch.cuda.synchronize()
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), step
+    assert torch.isnan(hint[1])          # short row: no guess
