@@ -310,6 +310,42 @@ def bench_extras(dev, lib, peak):
             small[f"B{B}_k{k}"] = round(_time_calls(lambda i: fast_topk_v3(s[i], lengths, k, out=o), n, 200, dev), 2)
             del s
     out["outlier_tail_us_L1M"] = small
+    # Threshold guesses carried from call to call (fast_topk_v3(threshold_hint=...)): the decode-stream
+    # use, where consecutive calls see similar rows.  Same inputs as above (the headline's 64 rotating
+    # rows; one ragged batch whose rows are perturbed from step to step), exact results either way.
+    from flash_float_jit_kernels_b200 import new_threshold_hint
+    hinted = {}
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def missed_steps(call, n, steps=24):
+        miss = 0
+        for i in range(steps):
+            status.zero_()
+            call(i % n)
+            miss += int(status.item()) != 0
+        return miss
+
+    rows = make_rows(64, L_SHARD, dev, seed=1)
+    lengths = torch.tensor([L_SHARD], dtype=torch.int32, device=dev)
+    o = torch.empty((1, K_TOP), dtype=torch.int32, device=dev)
+    hint = new_threshold_hint(1, dev)
+    call = lambda i: fast_topk_v3(rows[i:i + 1], lengths, K_TOP, out=o, status=status, threshold_hint=hint)
+    hinted["B1_L1M_us"] = round(_time_calls(call, 64, 400, dev), 2)
+    hinted["B1_L1M_missed_steps_of_24"] = missed_steps(call, 64)
+    del rows
+    s0, l0, _ = workloads.lightning_indexer_logits(64, 131072, 4096, seed=2, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    steps = [s0 + 0.02 * j * torch.randn(s0.shape, generator=g, device=dev) for j in range(9)]   # 302 MB > L2
+    o = torch.empty((64, K_TOP), dtype=torch.int32, device=dev)
+    hint = new_threshold_hint(64, dev)
+    plain = lambda i: fast_topk_v3(steps[i], l0, K_TOP, out=o)
+    call = lambda i: fast_topk_v3(steps[i], l0, K_TOP, out=o, status=status, threshold_hint=hint)
+    hinted["b64_ragged_plain_us"] = round(_time_calls(plain, 9, 90, dev), 2)
+    hinted["b64_ragged_us"] = round(_time_calls(call, 9, 90, dev), 2)
+    hinted["b64_ragged_rows_per_s"] = round(64 / (hinted["b64_ragged_us"] * 1e-6), 1)
+    hinted["b64_ragged_missed_steps_of_24"] = missed_steps(call, 9)
+    out["threshold_hint"] = hinted
     return out
 
 

@@ -90,15 +90,17 @@ void init_device(int device) {
   int prev = 0;
   cudaError_t e = cudaGetDevice(&prev);
   if (e == cudaSuccess && prev != device) e = cudaSetDevice(device);
-  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false>);
-  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePlain>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePush>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true, ff::kModePlain>);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(ff::cp_merge_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              ff::kMaxPeers * ff::kMaxK * static_cast<int>(sizeof(uint32_t)));
   if (e == cudaSuccess) {
-    g_max_cluster[device] = max_cluster_for(ff::topk_cluster_kernel<false>);
+    g_max_cluster[device] = max_cluster_for(ff::topk_cluster_kernel<false, ff::kModePlain>);
     for (int i = 0; i < 5; ++i)
-      g_active_clusters[device][i] = active_clusters_for(ff::topk_cluster_kernel<false>, 1 << i);
+      g_active_clusters[device][i] = active_clusters_for(ff::topk_cluster_kernel<false, ff::kModePlain>, 1 << i);
     int sms = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     g_sm_count[device] = sms > 0 ? sms : 148;
@@ -194,7 +196,14 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
 
-  cudaError_t e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP>, q);
+  // one instantiation per mode: the plain select carries no code of the others
+  cudaError_t e;
+  if (!HAS_MAP && q.push_world > 0)
+    e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePush>, q);
+  else if (!HAS_MAP && (q.hint_in != nullptr || q.hint_out != nullptr))
+    e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted>, q);
+  else
+    e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP, ff::kModePlain>, q);
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx(topk_cluster_kernel)");
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;

@@ -797,9 +797,10 @@ struct PushCtx {
   uint32_t step;
 };
 
+template <bool PUSH>
 __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, int row, int j, int32_t idx,
                                      uint32_t key, bool is_map, int table_row) {
-  if (p.push_world > 0) {
+  if (PUSH) {
     // one self-validating 8-byte entry per plane and peer: {payload, step}
     const uint32_t vbits = idx < 0 ? kNoCandidateBits : bits_of_key(key);
     const uint32_t gidx = idx < 0 ? 0xffffffffu : static_cast<uint32_t>(idx + p.shard_offset);
@@ -836,9 +837,18 @@ __device__ __forceinline__ float prefilter_value(uint32_t key_lo) {
   return __uint_as_float(bits_of_key(key_lo));
 }
 
-template <bool HAS_MAP>
+// MODE selects what is compiled in besides the plain select, so that the plain kernel
+// carries no code of the others: kModeHinted = threshold guesses (hint_in / hint_out),
+// kModePush = context-parallel send (and single-kernel step).
+constexpr int kModePlain = 0;
+constexpr int kModeHinted = 1;
+constexpr int kModePush = 2;
+
+template <bool HAS_MAP, int MODE>
 __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
                                               const PushCtx& push) {
+  constexpr bool kPush = MODE == kModePush;
+  constexpr bool kHinted = MODE == kModeHinted;
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
   uint32_t* merged = reinterpret_cast<uint32_t*>(smem + kSmemStage);
@@ -889,7 +899,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
   if (identity || len <= k) {
     if (my_share != 0) return;
-    if (!HAS_MAP && p.hint_out != nullptr && tid == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);   // no guess
+    if (kHinted && !HAS_MAP && p.hint_out != nullptr && tid == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);   // no guess
     if (!HAS_MAP && p.out_val != nullptr) {
       // Context-parallel shard shorter than k: every position is a candidate, but the
       // merge expects the run in canonical order, so rank the few elements by counting.
@@ -897,13 +907,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       __syncthreads();
       for (int j = tid; j < k; j += kThreads) {
         if (j >= len) {
-          emit(p, push, row, j, -1, 0u, false, table_row);
+          emit<kPush>(p, push, row, j, -1, 0u, false, table_row);
           continue;
         }
         const uint64_t c = stage[j];
         int pos = 0;
         for (int q = 0; q < len; ++q) pos += stage[q] > c ? 1 : 0;
-        emit(p, push, row, pos, comp_index(c), comp_key(c), false, table_row);
+        emit<kPush>(p, push, row, pos, comp_index(c), comp_key(c), false, table_row);
       }
       return;
     }
@@ -912,13 +922,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         // no more candidates than k slots: pass them through in position order
         const int64_t a = j < len ? seg_addr(j, p.seg_len, p.seg_stride) : 0;
         const int32_t idx = j < len ? imap[a] : -1;
-        emit(p, push, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
+        emit<kPush>(p, push, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
       } else {
         const int n = HAS_MAP ? glen : len;
         const bool v = j < n;
         uint32_t key = 0u;
         if (v && !HAS_MAP && p.out_val != nullptr) key = key_of(rowp[j]);
-        emit(p, push, row, j, v ? j : -1, key, HAS_MAP, table_row);
+        emit<kPush>(p, push, row, j, v ? j : -1, key, HAS_MAP, table_row);
       }
     }
     return;
@@ -1009,12 +1019,12 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   bool hinted_done = false;
   float hint = 0.f;
   bool use_hint = false;
-  if (!HAS_MAP && p.hint_in != nullptr) {
+  if (kHinted && !HAS_MAP && p.hint_in != nullptr) {
     hint = p.hint_in[row];
     use_hint = hint == hint;   // NaN: no guess
   }
   __syncthreads();
-  if (use_hint) {
+  if (kHinted && use_hint) {
     stream_pass(ts, [&](uint32_t tile, int tt, int units) {
       collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, hint, stage, kSortCap, &sh.stage_count);
     });
@@ -1251,9 +1261,9 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   if (ts.timed_out && p.status != nullptr && tid == 0) atomicOr(p.status, 2);
   if (!ok) {
     if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
-    if (!HAS_MAP && p.hint_out != nullptr && tid == 0 && my_share == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);
+    if (kHinted && !HAS_MAP && p.hint_out != nullptr && tid == 0 && my_share == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);
     if (my_share == 0) {
-      for (int j = tid; j < k; j += kThreads) emit(p, push, row, j, -1, 0u, HAS_MAP, table_row);
+      for (int j = tid; j < k; j += kThreads) emit<kPush>(p, push, row, j, -1, 0u, HAS_MAP, table_row);
     }
     return;
   }
@@ -1424,14 +1434,14 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
-    if (pos < k) emit(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (pos < k) emit<kPush>(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
   }
   // Next call's guess: a score of rank about 3k/2, so that about 3k/2 elements (between k and
   // 4096) pass it on similar data.  With T >= 3k/2 survivors it is the lower edge of the bucket
   // that holds that rank; with fewer it is extrapolated linearly below the smallest survivor
   // from the ranks T/2 and T.  Two lanes of the row's first CTA each find one bucket by a
   // binary search over the buckets' suffix counts (the same in every CTA).
-  if (!HAS_MAP && p.hint_out != nullptr && my_share == 0 && tid < 32) {
+  if (kHinted && !HAS_MAP && p.hint_out != nullptr && my_share == 0 && tid < 32) {
     const int want = k + (k >> 1);
     const int rank_a = min(T, want) - 1;
     const int rank_m = T >> 1;
@@ -1459,8 +1469,9 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   FF_TRACE(p, 25);
 }
 
-template <bool HAS_MAP>
+template <bool HAS_MAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
+  constexpr bool kPush = MODE == kModePush;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ ClusterShared sh;
   // Context-parallel send: this launch also delivers its result to the peers.  The step number is
@@ -1469,13 +1480,13 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
   push.off = 0;
   push.step = 0u;
   uint32_t* ctrl = nullptr;
-  if (!HAS_MAP && p.push_world > 0) {
+  if (kPush && !HAS_MAP && p.push_world > 0) {
     ctrl = p.push_peers.base[p.push_rank] + p.push_ctrl_offset;
     push.step = *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) + 1u;
     push.off = (static_cast<int64_t>(push.step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
   }
-  topk_row_body<HAS_MAP>(p, smem, sh, push);
-  if (!HAS_MAP && p.push_world > 0) {
+  topk_row_body<HAS_MAP, MODE>(p, smem, sh, push);
+  if (kPush && !HAS_MAP && p.push_world > 0) {
     // Every CTA read the step long ago; the one that counts itself last advances the counter.
     // A thread outside warp 0 does it, so that its round trip overlaps the merge below.
     if (threadIdx.x == 32) {
