@@ -19,8 +19,8 @@ from . import _lib, fast_topk_v3, workloads
 
 # slot -> name, in execution order (slots as written by FF_TRACE in csrc/ff_topk_kernel.cuh)
 STAGES = [
-    (0, "start"), (1, "sweep1_hist"), (26, "merge_barrier1"), (27, "merge_dsmem_loads"),
-    (28, "slice_scan"), (29, "merge_barrier2"), (30, "find_threshold"), (2, "merge_barrier3"),
+    (0, "start"), (1, "sweep1_hist"), (26, "merge_barrier"), (27, "merge_remote_loads"),
+    (28, "merge_scan"), (29, "merge_fine_loads"), (30, "merge_threshold"), (2, "merge_end"),
     (3, "sweep2_collect"), (4, "gather_to_peers"), (20, "final_barrier"), (22, "finish_bin_hist"),
     (23, "finish_scan"), (24, "finish_scatter"), (31, "finish_queue_units"), (25, "finish_rank_emit"),
 ]
@@ -34,8 +34,10 @@ CASES = {
 }
 
 
-def trace_once(score, lengths, k, cluster=0):
-    """Returns (cluster_size, int64 array [n_ctas, 32] of cycle stamps)."""
+def trace_once(score, lengths, k, cluster=0, hinted=False):
+    """Returns (cluster_size, int64 array [n_ctas, 32] of cycle stamps).  With ``hinted`` the
+    warm-up launches leave a threshold guess per row and the traced launch uses it (no histogram
+    stages then)."""
     lib = _lib.load()
     dev = score.device
     lib.ff_topk_set_cluster_override(cluster)
@@ -43,12 +45,16 @@ def trace_once(score, lengths, k, cluster=0):
     # a row may be split over up to 64 clusters of up to 16 CTAs: size the buffer for the largest grid
     buf = torch.zeros((score.shape[0] * 1024, 32), dtype=torch.int64, device=dev)
     out = torch.empty((score.shape[0], k), dtype=torch.int32, device=dev)
+    hint = None
+    if hinted:
+        from . import new_threshold_hint
+        hint = new_threshold_hint(score.shape[0], dev)
     for _ in range(3):
-        fast_topk_v3(score, lengths, k, out=out)
+        fast_topk_v3(score, lengths, k, out=out, threshold_hint=hint)
     torch.cuda.synchronize()
     lib.ff_topk_set_trace_buffer(buf.data_ptr())
     try:
-        fast_topk_v3(score, lengths, k, out=out)
+        fast_topk_v3(score, lengths, k, out=out, threshold_hint=hint)
         torch.cuda.synchronize()
     finally:
         lib.ff_topk_set_trace_buffer(None)
@@ -75,14 +81,16 @@ def main():
     ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--mhz", type=float, default=1965.0, help="SM clock used to convert cycles to us")
+    ap.add_argument("--hinted", action="store_true", help="trace a launch that uses a threshold guess")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     mhz = args.mhz
     names = sorted(CASES) if args.case == "all" else [args.case]
     for name in names:
         score, lengths, _, k = CASES[name](dev)
-        C, t = trace_once(score, lengths, k, args.cluster)
-        print(f"== {name}: B={score.shape[0]} L={score.shape[1]} k={k} cluster={C} ctas={t.shape[0]} (us at {mhz} MHz)")
+        C, t = trace_once(score, lengths, k, args.cluster, args.hinted)
+        print(f"== {name}{' (threshold guess)' if args.hinted else ''}: B={score.shape[0]} L={score.shape[1]} k={k} "
+              f"cluster={C} ctas={t.shape[0]} (us at {mhz} MHz)")
         for cta in sorted({0, t.shape[0] - 1}):
             print(f"  cta {cta}: {format_timeline(t[cta], mhz)}")
 
