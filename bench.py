@@ -346,6 +346,34 @@ def bench_extras(dev, lib, peak):
     hinted["b64_ragged_rows_per_s"] = round(64 / (hinted["b64_ragged_us"] * 1e-6), 1)
     hinted["b64_ragged_missed_steps_of_24"] = missed_steps(call, 9)
     out["threshold_hint"] = hinted
+    del steps, s0
+    # The step before the path: the indexer-logit producer (tcgen05 kernel) on the same ragged
+    # batch shape, from an fp8 K cache of 64 x 131072 keys (1 GiB, far larger than L2), alone and
+    # followed by the top-k.  Bound: the K bytes read once from HBM.
+    try:
+        from flash_float_jit_kernels_b200.indexer_logits import indexer_logits_fp8
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        B, Lm = 64, 131072
+        f8 = torch.float8_e4m3fn
+        q = (torch.randn((B, 64, 128), generator=g, device=dev) / 4).to(f8)
+        w = torch.rand((B, 64), generator=g, device=dev)
+        kc = torch.empty((B, Lm, 128), dtype=f8, device=dev)
+        for b in range(B):
+            kc[b] = (torch.randn((Lm, 128), generator=g, device=dev) / 4).to(f8)
+        sc = torch.full((B, Lm), float("-inf"), device=dev)
+        o = torch.empty((B, K_TOP), dtype=torch.int32, device=dev)
+        k_bytes = 128 * int(l0.sum())
+        us_p = _time_calls(lambda i: indexer_logits_fp8(q, kc, w, l0, out=sc), 1, 20, dev)
+        us_pt = _time_calls(lambda i: (indexer_logits_fp8(q, kc, w, l0, out=sc), fast_topk_v3(sc, l0, K_TOP, out=o)), 1, 20, dev)
+        out["indexer_logits_b64_ragged"] = {
+            "producer_us": round(us_p, 2), "k_cache_bytes_read": k_bytes,
+            "achieved_gbs": round(k_bytes / (us_p * 1e-6) / 1e9, 1),
+            "frac_of_measured_peak": round(k_bytes / (us_p * 1e-6) / 1e9 / peak, 4),
+            "producer_plus_topk_us": round(us_pt, 2)}
+        del kc, sc
+    except Exception as e:   # the producer is a separate library; its absence must not hide the top-k numbers
+        out["indexer_logits_b64_ragged"] = {"error": str(e)[:200]}
     return out
 
 

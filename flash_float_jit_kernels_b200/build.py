@@ -1,7 +1,8 @@
-"""In-tree build of the CUDA library (``csrc/libff_topk.so``) with nvcc.
+"""In-tree build of the CUDA libraries (``csrc/libff_topk.so`` and
+``csrc/libff_indexer.so``) with nvcc.
 
-The library is built for sm_100a only and kept beside its sources so the
-loader (``_lib.py``) finds it without any JIT cache.  Run as
+The libraries are built for sm_100a only and kept beside their sources so the
+loaders (``_lib.py``, ``indexer_logits.py``) find them without any JIT cache.  Run as
 ``python -m flash_float_jit_kernels_b200.build``.  The reference JIT-compiles
 at first call instead (``jit_kernel/topk_indexer.py:76-106``).
 """
@@ -18,6 +19,8 @@ INCLUDE = Path(__file__).resolve().parent.parent / "include"
 LIB_NAME = "libff_topk.so"
 SOURCES = ["ff_topk.cu"]
 HEADERS = ["ff_topk_common.cuh", "ff_topk_kernel.cuh", "ff_cp_exchange.cuh"]
+INDEXER_LIB_NAME = "libff_indexer.so"      # the logit producer: its own library and header
+INDEXER_SOURCES = ["ff_indexer_logits.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -28,6 +31,10 @@ NVCC_FLAGS = [
 
 def lib_path() -> Path:
     return CSRC / LIB_NAME
+
+
+def indexer_lib_path() -> Path:
+    return CSRC / INDEXER_LIB_NAME
 
 
 def _nvcc() -> str:
@@ -50,15 +57,11 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
-def build_library(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
-    """Compile ``csrc/*.cu`` into ``csrc/libff_topk.so`` (sm_100a)."""
-    out = lib_path()
-    if not force and not is_stale():
-        return out
+def _compile(out: Path, sources, verbose: bool, extra_flags) -> Path:
     cmd = [_nvcc(), *NVCC_FLAGS, *extra_flags]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(out)] + [str(CSRC / s) for s in SOURCES]
+    cmd += ["-o", str(out)] + [str(CSRC / s) for s in sources]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(res.stdout + res.stderr)
@@ -67,5 +70,23 @@ def build_library(force: bool = False, verbose: bool = False, extra_flags=()) ->
     return out
 
 
+def build_library(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
+    """Compile ``csrc/ff_topk.cu`` into ``csrc/libff_topk.so`` (sm_100a)."""
+    out = lib_path()
+    if not force and not is_stale():
+        return out
+    return _compile(out, SOURCES, verbose, extra_flags)
+
+
+def build_indexer_library(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
+    """Compile ``csrc/ff_indexer_logits.cu`` into ``csrc/libff_indexer.so`` (sm_100a)."""
+    out = indexer_lib_path()
+    deps = [CSRC / s for s in INDEXER_SOURCES] + [INCLUDE / "ff_indexer_logits.h"]
+    if not force and out.exists() and all(d.stat().st_mtime <= out.stat().st_mtime for d in deps):
+        return out
+    return _compile(out, INDEXER_SOURCES, verbose, extra_flags)
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_indexer_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,353 @@
+// Lightning-indexer logits for sm_100a: the step that produces the scores the
+// top-k indexer selects from,
+//     s[b, j] = sum_h w[b, h] * relu( q[b, h, :] . k[b, j, :] ),
+// 64 heads, head_dim 128, q and K in fp8 e4m3, fp32 accumulation.  The reference
+// has no such kernel; the shape is the one its README gives for the indexer
+// (README.md:28) and the benchmark's ragged decode batch is generated this way.
+//
+// One CTA works on one row b and a strided share of its 128-key tiles:
+//   * two producer warps copy a tile of K (128 keys x 128 bytes) into shared
+//     memory with 16-byte cp.async, writing the 128-byte-swizzled K-major layout
+//     the tensor core reads (16-byte chunk c of key r goes to chunk c ^ (r & 7));
+//     rows past the row's length are zero-filled, nothing outside K is read;
+//   * one thread issues four tcgen05.mma (kind::f8f6f4, M = 128 keys, N = 64
+//     heads, K = 32 per instruction) per tile into one of two accumulator
+//     buffers in tensor memory (128 lanes x 64 fp32 columns each);
+//   * four epilogue warps read their 32 lanes (one key per thread, its 64 head
+//     dot products) with tcgen05.ld, apply relu, weight and sum over the heads in
+//     head order with fused multiply-adds, and store one score per key.
+// Stages are handed over with mbarriers; every wait is bounded and sets a status
+// bit instead of spinning for ever.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/ff_indexer_logits.h"
+
+namespace ffl {
+
+constexpr int kHeads = 64;
+constexpr int kDim = 128;          // bytes per key and per head (fp8)
+constexpr int kTileKeys = 128;
+constexpr int kStages = 6;         // K tiles in flight
+constexpr int kTileBytes = kTileKeys * kDim;   // 16 KiB
+constexpr int kQBytes = kHeads * kDim;         // 8 KiB
+constexpr int kEpilogueWarps = 4;
+constexpr int kMmaWarp = 4;
+constexpr int kProducerWarp0 = 5;
+constexpr int kProducerWarps = 2;
+constexpr int kProducerThreads = kProducerWarps * 32;
+constexpr int kThreads = (kProducerWarp0 + kProducerWarps) * 32;   // 224
+constexpr int kTmemCols = 128;     // two accumulator buffers of 64 columns
+constexpr int kWaitLimit = 1 << 20;   // polls of one bounded wait; the first wait that runs out ends all others early
+
+// shared memory: [q 8 KiB][kStages x 16 KiB K tiles], 1024-byte aligned (swizzle atom)
+constexpr int kSmemQ = 0;
+constexpr int kSmemK = kQBytes;
+constexpr int kSmemBytes = kQBytes + kStages * kTileBytes + 1024;   // + alignment slack
+
+struct Params {
+  const uint8_t* q;       // [B, 64, 128] e4m3
+  const uint8_t* k;       // [B, k_row_stride] bytes, key j of row b at k + b * k_row_stride + j * 128
+  int64_t k_row_stride;   // bytes
+  const float* w;         // [B, 64]
+  const int32_t* lengths; // [B]
+  float* scores;          // [B, score_stride]
+  int64_t score_stride;   // elements
+  int32_t L_width;
+  int32_t* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: gives up after kWaitLimit polls, or as soon as another wait of this CTA has
+// given up (*gave_up != 0), and then records that itself.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* gave_up) {
+  for (int i = 0; i < kWaitLimit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((i & 255) == 255 && *gave_up != 0) break;
+  }
+  *gave_up = 1;
+  return false;
+}
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows at a
+// 128-byte pitch, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);    // start address, bits [0,14)
+  d |= static_cast<uint64_t>(1) << 16;                    // leading byte offset (unused with one swizzle atom along K)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;            // stride byte offset: 8 rows x 128 bytes
+  d |= static_cast<uint64_t>(1) << 46;                    // descriptor version for this architecture
+  d |= static_cast<uint64_t>(2) << 61;                    // layout type: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor: e4m3 x e4m3 -> f32, both operands K-major, M = 128, N = 64.
+constexpr uint32_t kInstrDesc = (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) |
+                                (static_cast<uint32_t>(kHeads >> 3) << 17) | (static_cast<uint32_t>(kTileKeys >> 4) << 24);
+
+__device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 consecutive fp32 columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Shared {
+  unsigned long long full[kStages];    // K tile landed (producer threads arrive)
+  unsigned long long empty[kStages];   // K tile consumed (tcgen05.commit arrives)
+  unsigned long long qfull;            // q landed
+  unsigned long long tfull[2];         // accumulator buffer complete (tcgen05.commit arrives)
+  unsigned long long tempty[2];        // accumulator buffer read out (epilogue threads arrive)
+  uint32_t tmem_base;
+  int timed_out;
+  float w[kHeads];
+};
+
+__global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ Shared sh;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
+  const uint32_t q_s = smem_base + kSmemQ;
+  const uint32_t k_s = smem_base + kSmemK;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int row = blockIdx.y;
+  int len = p.lengths[row];
+  if (len > p.L_width) len = p.L_width;
+  if (len < 0) len = 0;
+  const int n_tiles_row = (len + kTileKeys - 1) / kTileKeys;
+  // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int my_tiles = n_tiles_row > static_cast<int>(blockIdx.x)
+                           ? (n_tiles_row - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
+                           : 0;
+  if (my_tiles == 0) return;   // uniform over the CTA, before any barrier or allocation
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&sh.full[s]), kProducerThreads);
+      mbar_init(smem_u32(&sh.empty[s]), 1);
+    }
+    mbar_init(smem_u32(&sh.qfull), kProducerThreads);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh.tfull[b]), 1);
+      mbar_init(smem_u32(&sh.tempty[b]), kEpilogueWarps * 32);
+    }
+    sh.timed_out = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (tid < kHeads) sh.w[tid] = p.w[static_cast<int64_t>(row) * kHeads + tid];
+  if (warp == kMmaWarp) {   // one warp allocates the tensor memory columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+
+  if (warp >= kProducerWarp0) {
+    // ---------------- producers ----------------
+    const int pt = tid - kProducerWarp0 * 32;
+    const uint8_t* qrow = p.q + static_cast<int64_t>(row) * kQBytes;
+    for (int i = pt; i < kHeads * 8; i += kProducerThreads) {   // 64 heads x 8 chunks of 16 bytes
+      const int r = i >> 3, c = i & 7;
+      cp_async_16(q_s + r * kDim + ((c ^ (r & 7)) << 4), qrow + r * kDim + c * 16, 16u);
+    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    fence_async_proxy();
+    mbar_arrive(smem_u32(&sh.qfull));
+    const uint8_t* krow = p.k + static_cast<int64_t>(row) * p.k_row_stride;
+    // tile i of this CTA goes to stage i % kStages; its copies are waited for kStages - 1 tiles later
+    for (int i = 0; i < my_tiles + kStages - 1; ++i) {
+      if (i < my_tiles) {
+        const int stage = i % kStages;
+        if (i >= kStages) {   // the stage's previous tile must have been consumed
+          (void)mbar_wait(smem_u32(&sh.empty[stage]), static_cast<uint32_t>((i / kStages - 1) & 1), &sh.timed_out);
+        }
+        const int key0 = (static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) * kTileKeys;
+        const uint32_t dst = k_s + stage * kTileBytes;
+        for (int e = pt; e < kTileKeys * 8; e += kProducerThreads) {
+          const int r = e >> 3, c = e & 7;
+          const bool valid = key0 + r < len;
+          const uint8_t* src = krow + static_cast<int64_t>(valid ? key0 + r : 0) * kDim + c * 16;
+          cp_async_16(dst + r * kDim + ((c ^ (r & 7)) << 4), src, valid ? 16u : 0u);   // zero-fill past the end
+        }
+      }
+      cp_async_commit();   // an empty group keeps the group count in step with i
+      const int done = i - (kStages - 1);
+      if (done >= 0) {
+        cp_async_wait<kStages - 1>();   // tile `done` of this thread has landed
+        fence_async_proxy();
+        mbar_arrive(smem_u32(&sh.full[done % kStages]));
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ---------------- tensor-core issue (one thread) ----------------
+    if (lane == 0) {
+      (void)mbar_wait(smem_u32(&sh.qfull), 0u, &sh.timed_out);
+      for (int i = 0; i < my_tiles; ++i) {
+        const int stage = i % kStages;
+        const int buf = i & 1;
+        if (i >= 2) {   // the accumulator buffer's previous tile must have been read out
+          (void)mbar_wait(smem_u32(&sh.tempty[buf]), static_cast<uint32_t>((i / 2 - 1) & 1), &sh.timed_out);
+        }
+        (void)mbar_wait(smem_u32(&sh.full[stage]), static_cast<uint32_t>((i / kStages) & 1), &sh.timed_out);
+        tc_fence_after();
+        const uint32_t a_addr = k_s + stage * kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 32; ++ks) {   // 32 bytes of K per instruction, inside the swizzle atom
+          mma_f8(tmem + buf * kHeads, smem_desc(a_addr + ks * 32), smem_desc(q_s + ks * 32), ks > 0 ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&sh.empty[stage]));   // the K tile may be overwritten once these MMAs are done
+        mma_commit(smem_u32(&sh.tfull[buf]));     // ... and the accumulator is complete
+      }
+    }
+  } else {
+    // ---------------- epilogue: thread = key (tensor memory lane) ----------------
+    const int key_in_tile = warp * 32 + lane;
+    float* out_row = p.scores + static_cast<int64_t>(row) * p.score_stride;
+    for (int i = 0; i < my_tiles; ++i) {
+      const int buf = i & 1;
+      (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((i / 2) & 1), &sh.timed_out);
+      tc_fence_after();
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + buf * kHeads;
+      float s = 0.f;
+      float v[32];
+      tmem_ld32(taddr, v);
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[h], fmaxf(v[h], 0.f), s);
+      tmem_ld32(taddr + 32, v);
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[32 + h], fmaxf(v[h], 0.f), s);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.tempty[buf]));
+      const int key = (static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) * kTileKeys + key_in_tile;
+      if (key < p.L_width) out_row[key] = key < len ? s : __uint_as_float(0xff800000u);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  if (tid == 0 && sh.timed_out && p.status != nullptr) atomicOr(p.status, 2);
+}
+
+}  // namespace ffl
+
+namespace {
+thread_local char g_err[256] = "";
+int fail(int code, const char* msg) {
+  snprintf(g_err, sizeof(g_err), "%s", msg);
+  return code;
+}
+int fail_cuda(cudaError_t e, const char* where) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+  return static_cast<int>(e);
+}
+constexpr int kMaxDevices = 64;
+std::once_flag g_once[kMaxDevices];
+int g_rc[kMaxDevices];
+std::atomic<int64_t> g_launches{0};
+void init_device(int device) {
+  g_rc[device] = static_cast<int>(cudaFuncSetAttribute(ffl::indexer_logits_kernel,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, ffl::kSmemBytes));
+}
+}  // namespace
+
+extern "C" {
+
+const char* ff_indexer_last_error_string(void) { return g_err; }
+int64_t ff_indexer_launch_count(void) { return g_launches.load(); }
+
+int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_row_stride_bytes, const float* w,
+                             const int32_t* lengths, float* scores, int64_t score_stride, int32_t B,
+                             int32_t L_width, int32_t ctas_per_row, int32_t* status, void* stream) {
+  if (B < 0 || L_width < 0) return fail(-2, "negative B or L_width");
+  if (B == 0 || L_width == 0) return 0;
+  if (q_e4m3 == nullptr || k_e4m3 == nullptr || w == nullptr || lengths == nullptr || scores == nullptr)
+    return fail(-3, "q, k, w, lengths and scores must not be NULL");
+  if ((reinterpret_cast<uintptr_t>(q_e4m3) & 15u) != 0 || (reinterpret_cast<uintptr_t>(k_e4m3) & 15u) != 0 ||
+      (k_row_stride_bytes & 15) != 0)
+    return fail(-2, "q, k and the K row stride must be 16-byte aligned");
+  if (k_row_stride_bytes < static_cast<int64_t>(L_width) * ffl::kDim || score_stride < L_width)
+    return fail(-2, "row strides are smaller than the row");
+  if (B > 65535) return fail(-6, "B exceeds 65535 rows per launch");
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  if (device < 0 || device >= kMaxDevices) return fail(-2, "device ordinal out of range");
+  std::call_once(g_once[device], init_device, device);
+  if (g_rc[device] != 0) return fail_cuda(static_cast<cudaError_t>(g_rc[device]), "cudaFuncSetAttribute");
+  const int tiles = (L_width + ffl::kTileKeys - 1) / ffl::kTileKeys;
+  int per_row = ctas_per_row;
+  if (per_row <= 0) {   // about one wave of CTAs over the batch
+    int sms = 148;
+    (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    per_row = (2 * sms + B - 1) / B;
+  }
+  if (per_row > tiles) per_row = tiles;
+  if (per_row < 1) per_row = 1;
+  ffl::Params p;
+  p.q = static_cast<const uint8_t*>(q_e4m3);
+  p.k = static_cast<const uint8_t*>(k_e4m3);
+  p.k_row_stride = k_row_stride_bytes;
+  p.w = w;
+  p.lengths = lengths;
+  p.scores = scores;
+  p.score_stride = score_stride;
+  p.L_width = L_width;
+  p.status = status;
+  ffl::indexer_logits_kernel<<<dim3(per_row, B, 1), ffl::kThreads, ffl::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "indexer_logits_kernel");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
+}
+
+}  // extern "C"

@@ -93,8 +93,8 @@ def topk_numpy(score: np.ndarray, lengths: np.ndarray, k: int,
 def build_c(force: bool = False) -> Path:
     src = HERE / "oracle_topk.c"
     if force or not _LIB_PATH.exists() or _LIB_PATH.stat().st_mtime < src.stat().st_mtime:
-        subprocess.run(["gcc", "-O2", "-fPIC", "-std=c11", "-shared", "-o", str(_LIB_PATH), str(src)],
-                       check=True)
+        subprocess.run(["gcc", "-O2", "-fPIC", "-std=c11", "-ffp-contract=off", "-shared", "-o", str(_LIB_PATH),
+                        str(src), "-lm"], check=True)
     return _LIB_PATH
 
 
@@ -110,6 +110,9 @@ def _c():
         lib.oracle_topk_transform.argtypes = [
             ctypes.c_void_p, ctypes.c_int64, i32p, i32p, i32p, ctypes.c_int32, ctypes.c_int64,
             ctypes.c_int32, ctypes.c_int32, i32p, ctypes.c_int64, i32p, ctypes.c_int32, i32p]
+        lib.oracle_indexer_logits.restype = ctypes.c_int
+        lib.oracle_indexer_logits.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                              ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
         lib.oracle_key_of_bits.restype = ctypes.c_uint32
         lib.oracle_key_of_bits.argtypes = [ctypes.c_uint32]
         _clib = lib
@@ -209,3 +212,19 @@ def cp_merge(cand_val: np.ndarray, cand_idx: np.ndarray, lengths: np.ndarray, k:
         order = np.argsort(comp)[::-1][:k]
         out[b, :len(order)] = g[order]
     return out
+
+
+def indexer_logits(q: np.ndarray, k: np.ndarray, w: np.ndarray):
+    """One row of lightning-indexer logits: q [64, 128], k [n, 128] (fp8 e4m3 values widened to
+    float32), w [64] -> (scores float32 [n], number of dot products not exact in float32)."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    k = np.ascontiguousarray(k, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    assert q.shape == (64, 128) and k.ndim == 2 and k.shape[1] == 128 and w.shape == (64,)
+    out = np.empty(k.shape[0], dtype=np.float32)
+    bad = ctypes.c_int64(0)
+    rc = _c().oracle_indexer_logits(q.ctypes.data, k.ctypes.data, w.ctypes.data, k.shape[0], out.ctypes.data,
+                                    ctypes.byref(bad))
+    if rc != 0:
+        raise RuntimeError(f"oracle_indexer_logits failed: {rc}")
+    return out, int(bad.value)

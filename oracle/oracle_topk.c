@@ -120,3 +120,32 @@ int oracle_topk(const float* scores, int64_t row_stride, const int32_t* lengths,
 }
 
 uint32_t oracle_key_of_bits(uint32_t u) { return key_of_bits(u); }
+
+/* ---- lightning-indexer logits (checker for csrc/ff_indexer_logits.cu) -------------
+ * scores[j] = sum_h w[h] * relu(q[h,:] . k[j,:]), 64 heads, head_dim 128; q and k are
+ * fp8 e4m3 values already widened to float (every such value is a multiple of 2^-9).
+ * The dot product is summed in double, which is exact for 128 products of such values,
+ * and `*inexact` counts the dot products that are not representable in float (none
+ * for the seeded workloads: then every fp32 summation order gives this same value).
+ * The heads are summed in index order with fmaf, as the kernel does.  The operation
+ * is the one the reference's README names for its indexer (README.md:28). */
+#include <math.h>
+int oracle_indexer_logits(const float* q, const float* k, const float* w, int64_t n_keys,
+                          float* out, int64_t* inexact) {
+  int64_t bad = 0;
+  for (int64_t j = 0; j < n_keys; ++j) {
+    const float* kj = k + j * 128;
+    float s = 0.0f;
+    for (int h = 0; h < 64; ++h) {
+      const float* qh = q + h * 128;
+      double acc = 0.0;
+      for (int d = 0; d < 128; ++d) acc += (double)qh[d] * (double)kj[d];
+      const float dot = (float)acc;
+      if ((double)dot != acc) ++bad;
+      s = fmaf(w[h], dot > 0.0f ? dot : 0.0f, s);
+    }
+    out[j] = s;
+  }
+  if (inexact) *inexact = bad;
+  return 0;
+}
