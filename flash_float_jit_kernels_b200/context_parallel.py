@@ -12,10 +12,11 @@ Three steps per call, all on the current stream:
   3. exact merge-select of the ``P*k`` candidates.
 
 Two exchanges are implemented.  ``p2p`` (default on GPUs): every rank stores its
-block straight into every peer's receive buffer over NVLink (peer memory mapped
-through CUDA IPC) and raises a flag there; the merge kernel waits on its local
-flags with a bounded wait -- three kernel launches per step, no collective
-library call (``ff_topk_cp_step``).  ``nccl``: ``all_gather_into_tensor`` between
+candidates straight into every peer's receive buffer over NVLink (peer memory
+mapped through CUDA IPC) as self-validating 8-byte entries ``{payload, step}``,
+and the same kernel then polls its own (local) entries with a bounded wait and
+merges -- one kernel launch per step, no fence, no flag, no collective library
+call (``ff_topk_cp_step``).  ``nccl``: ``all_gather_into_tensor`` between
 ``ff_topk_cp_local`` and ``ff_topk_cp_merge``; kept as the baseline and as the
 fallback when peer memory cannot be mapped.
 

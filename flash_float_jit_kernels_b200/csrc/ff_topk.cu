@@ -609,7 +609,7 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
   for (int p = 0; p < ex->world; ++p)
     if (ex->peer[p] == nullptr) return fail(FF_ERR_NULL, "exchange: a peer is not mapped yet");
   // One launch: the shard-local select writes its k candidates per row straight into every
-  // peer's receive slot and the last CTA raises the flags (no separate push kernel).
+  // peer's receive slot as self-validating entries (no separate push kernel, no flags).
   int rc = check_common(ex->B, L_width, ex->k);
   if (rc != 0) return rc;
   if (scores == nullptr || lengths == nullptr) return fail(FF_ERR_NULL, "scores and lengths must not be NULL");

@@ -788,14 +788,15 @@ __device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C
   FF_TRACE(p, 30);
 }
 
-// Writes output slot j of `row` from a window-relative index (or -1) and key.
-// In push mode (context-parallel send) the slot is not written locally at all: the (value,
-// global index) pair goes straight into this rank's slot of every peer's receive buffer.
 // Context-parallel send: the step of this launch and where its entries go in a peer's buffer.
 struct PushCtx {
   int64_t off;     // words from a peer's base to this rank's slot of this step's parity
   uint32_t step;
 };
+
+// Writes output slot j of `row` from a window-relative index (or -1) and key.
+// In push mode (context-parallel send) the slot is not written locally at all: the (value,
+// global index) pair goes straight into this rank's slot of every peer's receive buffer.
 
 template <bool PUSH>
 __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, int row, int j, int32_t idx,

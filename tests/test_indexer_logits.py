@@ -8,8 +8,6 @@ import pytest
 import torch
 
 ROOT = Path(__file__).resolve().parents[1]
-import os
-_UNVERIFIED = pytest.mark.skipif(os.environ.get("FF_TEST_INDEXER") != "1", reason="producer kernel not yet verified on a GPU")
 
 
 def _declared():
@@ -53,7 +51,6 @@ def _make(B, L, seed, device):
     return q, k, w
 
 
-@_UNVERIFIED
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,L,lens,ctas", [(1, 128, [128], 1), (2, 1000, [1000, 37], 0), (3, 5000, [5000, 4097, 129], 3),
                                            (2, 20000, [20000, 1], 0)])
@@ -76,7 +73,6 @@ def test_logits_are_bit_exact_against_the_oracle(oracle, B, L, lens, ctas):
         assert np.all(np.isneginf(got[b, n:]))
 
 
-@_UNVERIFIED
 @pytest.mark.gpu
 def test_logits_feed_the_indexer(oracle):
     """Producer and selector back to back: the top-k of the produced scores is the oracle's
