@@ -58,6 +58,7 @@ struct Params {
   float* scores;          // [B, score_stride]
   int64_t score_stride;   // elements
   int32_t L_width;
+  int32_t tiles_per_cta;  // target share of a CTA, in 128-key tiles
   int32_t* status;
 };
 
@@ -159,10 +160,14 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
   if (len > p.L_width) len = p.L_width;
   if (len < 0) len = 0;
   const int n_tiles_row = (len + kTileKeys - 1) / kTileKeys;
-  // this CTA's tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
-  const int my_tiles = n_tiles_row > static_cast<int>(blockIdx.x)
-                           ? (n_tiles_row - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)
-                           : 0;
+  // Ragged batches: a row uses as many of the grid's CTAs as give each about p.tiles_per_cta
+  // tiles (the lengths live on the device, so the grid is sized for the longest possible row
+  // and the CTAs a short row does not need leave at once).  CTA x of the n_ctas works on tiles
+  // x, x + n_ctas, ...
+  int n_ctas = (n_tiles_row + p.tiles_per_cta - 1) / p.tiles_per_cta;
+  if (n_ctas > static_cast<int>(gridDim.x)) n_ctas = static_cast<int>(gridDim.x);
+  const int cta = static_cast<int>(blockIdx.x);
+  const int my_tiles = cta < n_ctas ? (n_tiles_row - cta + n_ctas - 1) / n_ctas : 0;
   if (my_tiles == 0) return;   // uniform over the CTA, before any barrier or allocation
 
   if (tid == 0) {
@@ -208,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
         if (i >= kStages) {   // the stage's previous tile must have been consumed
           (void)mbar_wait(smem_u32(&sh.empty[stage]), static_cast<uint32_t>((i / kStages - 1) & 1), &sh.timed_out);
         }
-        const int key0 = (static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) * kTileKeys;
+        const int key0 = (cta + i * n_ctas) * kTileKeys;
         const uint32_t dst = k_s + stage * kTileBytes;
         for (int e = pt; e < kTileKeys * 8; e += kProducerThreads) {
           const int r = e >> 3, c = e & 7;
@@ -265,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
       for (int h = 0; h < 32; ++h) s = fmaf(sh.w[32 + h], fmaxf(v[h], 0.f), s);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.tempty[buf]));
-      const int key = (static_cast<int>(blockIdx.x) + i * static_cast<int>(gridDim.x)) * kTileKeys + key_in_tile;
+      const int key = (cta + i * n_ctas) * kTileKeys + key_in_tile;
       if (key < p.L_width) out_row[key] = key < len ? s : __uint_as_float(0xff800000u);
     }
   }
@@ -325,14 +330,23 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   std::call_once(g_once[device], init_device, device);
   if (g_rc[device] != 0) return fail_cuda(static_cast<cudaError_t>(g_rc[device]), "cudaFuncSetAttribute");
   const int tiles = (L_width + ffl::kTileKeys - 1) / ffl::kTileKeys;
+  // Automatic: shares of about 32 tiles (512 KiB of K), but at least about four CTAs per SM in
+  // total when every row is full, so that small batches still fill the device.
   int per_row = ctas_per_row;
-  if (per_row <= 0) {   // about one wave of CTAs over the batch
+  int tiles_per_cta = 32;
+  if (per_row <= 0) {
     int sms = 148;
     (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-    per_row = (2 * sms + B - 1) / B;
+    const int want_ctas = (4 * sms + B - 1) / B;             // per row
+    if (tiles_per_cta * want_ctas > tiles) tiles_per_cta = (tiles + want_ctas - 1) / want_ctas;
+    if (tiles_per_cta < 1) tiles_per_cta = 1;
+    per_row = (tiles + tiles_per_cta - 1) / tiles_per_cta;
+  } else {
+    tiles_per_cta = (tiles + per_row - 1) / per_row;
   }
   if (per_row > tiles) per_row = tiles;
   if (per_row < 1) per_row = 1;
+  if (per_row > 65535) return fail(-6, "too many CTAs per row");
   ffl::Params p;
   p.q = static_cast<const uint8_t*>(q_e4m3);
   p.k = static_cast<const uint8_t*>(k_e4m3);
@@ -342,6 +356,7 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   p.scores = scores;
   p.score_stride = score_stride;
   p.L_width = L_width;
+  p.tiles_per_cta = tiles_per_cta;
   p.status = status;
   ffl::indexer_logits_kernel<<<dim3(per_row, B, 1), ffl::kThreads, ffl::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
