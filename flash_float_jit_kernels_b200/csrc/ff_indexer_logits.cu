@@ -83,6 +83,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   *gave_up = 1;
   return false;
 }
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
@@ -283,6 +290,279 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
   if (tid == 0 && sh.timed_out && p.status != nullptr) atomicOr(p.status, 2);
 }
 
+
+// ---- persistent variant ---------------------------------------------------------
+// The grid is two CTAs per SM whatever the batch; the work is cut into units of
+// kUnitTiles consecutive 128-key tiles of one row, numbered row by row (a prefix sum
+// over the rows' unit counts, computed by every CTA from the device-side lengths), and
+// CTA c takes units c, c + grid, c + 2 grid, ...  Barriers, tensor memory and the
+// pipeline state are set up once per CTA and run on across units; q is double buffered
+// (the next unit's q lands while the current unit's tiles are multiplied).
+constexpr int kUnitTiles = 8;
+constexpr int kPStages = 5;
+constexpr int kMaxRowsPersistent = 1024;
+constexpr int kPSmemQ = 0;                       // two q buffers
+constexpr int kPSmemK = 2 * kQBytes;
+constexpr int kPSmemBytes = 2 * kQBytes + kPStages * kTileBytes + 1024;
+
+struct PShared {
+  unsigned long long full[kPStages];
+  unsigned long long empty[kPStages];
+  unsigned long long qfull[2];
+  unsigned long long qempty[2];
+  unsigned long long tfull[2];
+  unsigned long long tempty[2];
+  uint32_t tmem_base;
+  int timed_out;
+  float w[kHeads];                       // head weights of the unit the epilogue is working on
+  int prefix[kMaxRowsPersistent + 1];    // units before row b
+};
+
+// One unit of work and the position inside it; every role walks the same sequence.
+struct UnitCursor {
+  int u;        // unit number (global), advanced by the grid size
+  int n;        // how many units this CTA has started before this one
+  int row, len, tile0, ntile;
+  int i;        // tile inside the unit
+  int t;        // tiles this CTA has passed before this one (drives stages and phases)
+};
+
+__device__ __forceinline__ int clamp_len(const Params& p, int row) {
+  int len = p.lengths[row];
+  if (len > p.L_width) len = p.L_width;
+  return len < 0 ? 0 : len;
+}
+
+__device__ __forceinline__ void cursor_load_unit(UnitCursor& c, const Params& p, const int* prefix, int B) {
+  int lo = 0, hi = B;   // last row with prefix[row] <= u
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= c.u) lo = mid; else hi = mid;
+  }
+  c.row = lo;
+  c.len = clamp_len(p, lo);
+  const int tiles_row = (c.len + kTileKeys - 1) / kTileKeys;
+  c.tile0 = (c.u - prefix[lo]) * kUnitTiles;
+  c.ntile = min(kUnitTiles, tiles_row - c.tile0);
+  c.i = 0;
+}
+// Moves to the next tile; returns false when the CTA's units are used up.
+__device__ __forceinline__ bool cursor_next(UnitCursor& c, const Params& p, const int* prefix, int B, int total_units,
+                                            int stride) {
+  c.t += 1;
+  c.i += 1;
+  if (c.i < c.ntile) return true;
+  c.u += stride;
+  c.n += 1;
+  if (c.u >= total_units) return false;
+  cursor_load_unit(c, p, prefix, B);
+  return true;
+}
+
+__global__ void __launch_bounds__(kThreads, 2) indexer_logits_persistent_kernel(const Params p, const int B) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ PShared sh;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t q_s = smem_base + kPSmemQ;
+  const uint32_t k_s = smem_base + kPSmemK;
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // units per row -> exclusive prefix (one warp: each lane sums a contiguous run of rows)
+  for (int b = tid; b < B; b += kThreads) {
+    const int tiles = (clamp_len(p, b) + kTileKeys - 1) / kTileKeys;
+    sh.prefix[b + 1] = (tiles + kUnitTiles - 1) / kUnitTiles;
+  }
+  if (tid == 0) {
+    sh.prefix[0] = 0;
+    for (int s = 0; s < kPStages; ++s) {
+      mbar_init(smem_u32(&sh.full[s]), kProducerThreads);
+      mbar_init(smem_u32(&sh.empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh.qfull[b]), kProducerThreads);
+      mbar_init(smem_u32(&sh.qempty[b]), 1);
+      mbar_init(smem_u32(&sh.tfull[b]), 1);
+      mbar_init(smem_u32(&sh.tempty[b]), kEpilogueWarps * 32);
+    }
+    sh.timed_out = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int per = (B + 31) / 32;
+    const int b0 = lane * per;
+    int sum = 0;
+    for (int j = 0; j < per; ++j)
+      if (b0 + j < B) sum += sh.prefix[b0 + j + 1];
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += v;
+    }
+    int running = incl - sum;
+    for (int j = 0; j < per; ++j) {
+      if (b0 + j < B) {
+        running += sh.prefix[b0 + j + 1];
+        sh.prefix[b0 + j + 1] = running;
+      }
+    }
+  }
+  __syncthreads();
+  const int total_units = sh.prefix[B];
+  const int stride = static_cast<int>(gridDim.x);
+  if (static_cast<int>(blockIdx.x) >= total_units) return;   // uniform, before the allocation
+
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh.tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+
+  UnitCursor c;
+  c.u = static_cast<int>(blockIdx.x);
+  c.n = 0;
+  c.t = 0;
+  cursor_load_unit(c, p, sh.prefix, B);
+
+  if (warp >= kProducerWarp0) {
+    // ---------------- producers ----------------
+    const int pt = tid - kProducerWarp0 * 32;
+    // Every tile is one copy group.  A tile is announced (its "full" barrier, and with a unit's
+    // first tile the unit's q) once its group has landed: normally when kPStages tiles are
+    // outstanding, the oldest is waited for; at the end, and before a wait that the tensor-core
+    // thread can only satisfy after seeing tiles still unannounced, everything outstanding is.
+    UnitCursor d = c;          // the next tile to announce
+    bool more = true;          // c points at a tile to issue
+    int lag = 0;               // tiles issued and not yet announced
+    auto announce_one = [&]() {
+      if (d.i == 0) mbar_arrive(smem_u32(&sh.qfull[d.n & 1]));
+      mbar_arrive(smem_u32(&sh.full[d.t % kPStages]));
+      lag -= 1;
+      (void)cursor_next(d, p, sh.prefix, B, total_units, stride);
+    };
+    auto announce_all = [&]() {
+      cp_async_wait<0>();
+      fence_async_proxy();
+      while (lag > 0) announce_one();
+    };
+    while (more) {
+      const int stage = c.t % kPStages;
+      if (c.t >= kPStages)
+        (void)mbar_wait(smem_u32(&sh.empty[stage]), static_cast<uint32_t>((c.t / kPStages - 1) & 1), &sh.timed_out);
+      if (c.i == 0) {   // first tile of a unit: its q goes into the same copy group
+        const int qb = c.n & 1;
+        if (c.n >= 2) {
+          // The buffer's previous unit (n - 2) must be multiplied.  After a short unit n - 1 some of
+          // its tiles may still be unannounced: announce them before waiting.
+          const uint32_t bar = smem_u32(&sh.qempty[qb]);
+          const uint32_t parity = static_cast<uint32_t>((c.n / 2 - 1) & 1);
+          if (!mbar_test(bar, parity)) {
+            announce_all();
+            (void)mbar_wait(bar, parity, &sh.timed_out);
+          }
+        }
+        const uint8_t* qrow = p.q + static_cast<int64_t>(c.row) * kQBytes;
+        for (int e = pt; e < kHeads * 8; e += kProducerThreads) {
+          const int rr = e >> 3, ch = e & 7;
+          cp_async_16(q_s + qb * kQBytes + rr * kDim + ((ch ^ (rr & 7)) << 4), qrow + rr * kDim + ch * 16, 16u);
+        }
+      }
+      const uint8_t* krow = p.k + static_cast<int64_t>(c.row) * p.k_row_stride;
+      const int key0 = (c.tile0 + c.i) * kTileKeys;
+      const uint32_t dst = k_s + stage * kTileBytes;
+      for (int e = pt; e < kTileKeys * 8; e += kProducerThreads) {
+        const int rr = e >> 3, ch = e & 7;
+        const bool valid = key0 + rr < c.len;
+        const uint8_t* src = krow + static_cast<int64_t>(valid ? key0 + rr : 0) * kDim + ch * 16;
+        cp_async_16(dst + rr * kDim + ((ch ^ (rr & 7)) << 4), src, valid ? 16u : 0u);
+      }
+      cp_async_commit();
+      lag += 1;
+      more = cursor_next(c, p, sh.prefix, B, total_units, stride);
+      if (lag == kPStages) {
+        cp_async_wait<kPStages - 1>();   // the oldest of the kPStages outstanding groups has landed
+        fence_async_proxy();
+        announce_one();
+      }
+    }
+    announce_all();
+  } else if (warp == kMmaWarp) {
+    // ---------------- tensor-core issue (one thread) ----------------
+    if (lane == 0) {
+      bool more = true;
+      while (more) {
+        const int stage = c.t % kPStages;
+        const int buf = c.t & 1;
+        const int qb = c.n & 1;
+        if (c.i == 0) (void)mbar_wait(smem_u32(&sh.qfull[qb]), static_cast<uint32_t>((c.n / 2) & 1), &sh.timed_out);
+        if (c.t >= 2) (void)mbar_wait(smem_u32(&sh.tempty[buf]), static_cast<uint32_t>((c.t / 2 - 1) & 1), &sh.timed_out);
+        (void)mbar_wait(smem_u32(&sh.full[stage]), static_cast<uint32_t>((c.t / kPStages) & 1), &sh.timed_out);
+        tc_fence_after();
+        const uint32_t a_addr = k_s + stage * kTileBytes;
+        const uint32_t b_addr = q_s + qb * kQBytes;
+#pragma unroll
+        for (int ks = 0; ks < kDim / 32; ++ks)
+          mma_f8(tmem + buf * kHeads, smem_desc(a_addr + ks * 32), smem_desc(b_addr + ks * 32), ks > 0 ? 1u : 0u);
+        mma_commit(smem_u32(&sh.empty[stage]));
+        mma_commit(smem_u32(&sh.tfull[buf]));
+        if (c.i == c.ntile - 1) mma_commit(smem_u32(&sh.qempty[qb]));   // the unit's q buffer is free after these MMAs
+        more = cursor_next(c, p, sh.prefix, B, total_units, stride);
+      }
+    }
+  } else {
+    // ---------------- epilogue: thread = key (tensor memory lane) ----------------
+    const int key_in_tile = warp * 32 + lane;
+    float w_next = p.w[static_cast<int64_t>(c.row) * kHeads + (tid & (kHeads - 1))];
+    bool more = true;
+    while (more) {
+      if (c.i == 0) {
+        // hand the head weights of this unit's row to all epilogue threads; the next unit's are fetched early
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // everyone is done with the previous unit's weights
+        if (tid < kHeads) sh.w[tid] = w_next;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int u_next = c.u + stride;
+        if (u_next < total_units) {
+          UnitCursor peek = c;
+          peek.u = u_next;
+          cursor_load_unit(peek, p, sh.prefix, B);
+          w_next = p.w[static_cast<int64_t>(peek.row) * kHeads + (tid & (kHeads - 1))];
+        }
+      }
+      const int buf = c.t & 1;
+      (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((c.t / 2) & 1), &sh.timed_out);
+      tc_fence_after();
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + buf * kHeads;
+      float s = 0.f;
+      float v[32];
+      tmem_ld32(taddr, v);
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[h], fmaxf(v[h], 0.f), s);
+      tmem_ld32(taddr + 32, v);
+#pragma unroll
+      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[32 + h], fmaxf(v[h], 0.f), s);
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh.tempty[buf]));
+      const int key = (c.tile0 + c.i) * kTileKeys + key_in_tile;
+      if (key < p.L_width)
+        p.scores[static_cast<int64_t>(c.row) * p.score_stride + key] = key < c.len ? s : __uint_as_float(0xff800000u);
+      more = cursor_next(c, p, sh.prefix, B, total_units, stride);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  if (tid == 0 && sh.timed_out && p.status != nullptr) atomicOr(p.status, 2);
+}
+
 }  // namespace ffl
 
 namespace {
@@ -300,8 +580,12 @@ std::once_flag g_once[kMaxDevices];
 int g_rc[kMaxDevices];
 std::atomic<int64_t> g_launches{0};
 void init_device(int device) {
-  g_rc[device] = static_cast<int>(cudaFuncSetAttribute(ffl::indexer_logits_kernel,
-                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, ffl::kSmemBytes));
+  cudaError_t e = cudaFuncSetAttribute(ffl::indexer_logits_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       ffl::kSmemBytes);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(ffl::indexer_logits_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             ffl::kPSmemBytes);
+  g_rc[device] = static_cast<int>(e);
 }
 }  // namespace
 
@@ -330,8 +614,32 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   std::call_once(g_once[device], init_device, device);
   if (g_rc[device] != 0) return fail_cuda(static_cast<cudaError_t>(g_rc[device]), "cudaFuncSetAttribute");
   const int tiles = (L_width + ffl::kTileKeys - 1) / ffl::kTileKeys;
-  // Automatic: shares of about 32 tiles (512 KiB of K), but at least about four CTAs per SM in
-  // total when every row is full, so that small batches still fill the device.
+  ffl::Params p;
+  p.q = static_cast<const uint8_t*>(q_e4m3);
+  p.k = static_cast<const uint8_t*>(k_e4m3);
+  p.k_row_stride = k_row_stride_bytes;
+  p.w = w;
+  p.lengths = lengths;
+  p.scores = scores;
+  p.score_stride = score_stride;
+  p.L_width = L_width;
+  p.tiles_per_cta = 0;
+  p.status = status;
+  if (ctas_per_row <= 0 && B <= ffl::kMaxRowsPersistent) {
+    // Automatic: the persistent kernel, two CTAs per SM, units of 8 tiles dealt out round robin.
+    int sms = 148;
+    (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int64_t max_units = static_cast<int64_t>(B) * ((tiles + ffl::kUnitTiles - 1) / ffl::kUnitTiles);
+    const int grid = static_cast<int>(max_units < 2 * sms ? max_units : 2 * sms);
+    ffl::indexer_logits_persistent_kernel<<<grid, ffl::kThreads, ffl::kPSmemBytes, static_cast<cudaStream_t>(stream)>>>(p, B);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail_cuda(e, "indexer_logits_persistent_kernel");
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return 0;
+  }
+  // A fixed number of CTAs per row (or a batch too large for the persistent kernel's row table):
+  // shares of about 32 tiles (512 KiB of K), but at least about four CTAs per SM in total when
+  // every row is full, so that small batches still fill the device.
   int per_row = ctas_per_row;
   int tiles_per_cta = 32;
   if (per_row <= 0) {
@@ -347,17 +655,7 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   if (per_row > tiles) per_row = tiles;
   if (per_row < 1) per_row = 1;
   if (per_row > 65535) return fail(-6, "too many CTAs per row");
-  ffl::Params p;
-  p.q = static_cast<const uint8_t*>(q_e4m3);
-  p.k = static_cast<const uint8_t*>(k_e4m3);
-  p.k_row_stride = k_row_stride_bytes;
-  p.w = w;
-  p.lengths = lengths;
-  p.scores = scores;
-  p.score_stride = score_stride;
-  p.L_width = L_width;
   p.tiles_per_cta = tiles_per_cta;
-  p.status = status;
   ffl::indexer_logits_kernel<<<dim3(per_row, B, 1), ffl::kThreads, ffl::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "indexer_logits_kernel");
