@@ -6,7 +6,7 @@
 // (README.md:28) and the benchmark's ragged decode batch is generated this way.
 //
 // One CTA works on one row b and a strided share of its 128-key tiles:
-//   * two producer warps copy a tile of K (128 keys x 128 bytes) into shared
+//   * four producer warps copy a tile of K (128 keys x 128 bytes) into shared
 //     memory with 16-byte cp.async, writing the 128-byte-swizzled K-major layout
 //     the tensor core reads (16-byte chunk c of key r goes to chunk c ^ (r & 7));
 //     rows past the row's length are zero-filled, nothing outside K is read;
@@ -14,8 +14,8 @@
 //     heads, K = 32 per instruction) per tile into one of two accumulator
 //     buffers in tensor memory (128 lanes x 64 fp32 columns each);
 //   * four epilogue warps read their 32 lanes (one key per thread, its 64 head
-//     dot products) with tcgen05.ld, apply relu, weight and sum over the heads in
-//     head order with fused multiply-adds, and store one score per key.
+//     dot products) with tcgen05.ld, apply relu, weight and sum over the heads with
+//     fused multiply-adds (four interleaved partial sums), and store one score per key.
 // Stages are handed over with mbarriers; every wait is bounded and sets a status
 // bit instead of spinning for ever.
 #include <cuda_runtime.h>
@@ -38,9 +38,9 @@ constexpr int kQBytes = kHeads * kDim;         // 8 KiB
 constexpr int kEpilogueWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kProducerWarp0 = 5;
-constexpr int kProducerWarps = 2;
+constexpr int kProducerWarps = 4;
 constexpr int kProducerThreads = kProducerWarps * 32;
-constexpr int kThreads = (kProducerWarp0 + kProducerWarps) * 32;   // 224
+constexpr int kThreads = (kProducerWarp0 + kProducerWarps) * 32;   // 288
 constexpr int kTmemCols = 128;     // two accumulator buffers of 64 columns
 constexpr int kWaitLimit = 1 << 20;   // polls of one bounded wait; the first wait that runs out ends all others early
 
@@ -100,6 +100,30 @@ __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Copies `rows` (a multiple of kProducerThreads / 8) rows of 128 bytes from global memory into the
+// 128-byte-swizzled layout at `dst` with all producer threads: thread pt takes chunk pt & 7 of
+// rows (pt >> 3) + (kProducerThreads / 8) * j.  The row step is a multiple of 8, so the swizzle term
+// (row & 7) is the same for all of a thread's rows and both addresses advance by a constant.
+// Rows at or beyond rows_valid are zero-filled and not read.
+template <int kRows>
+__device__ __forceinline__ void copy_rows_swizzled(uint32_t dst, const uint8_t* src, int pt, int rows_valid) {
+  constexpr int kRowStep = kProducerThreads / 8;
+  static_assert(kRowStep % 8 == 0 && kRows % kRowStep == 0, "producer thread count must keep (row & 7) fixed per thread");
+  const int r0 = pt >> 3, ch = pt & 7;
+  const uint32_t d0 = dst + r0 * kDim + ((ch ^ (r0 & 7)) << 4);
+  const uint8_t* s0 = src + r0 * kDim + ch * 16;
+  if (rows_valid >= kRows) {
+#pragma unroll
+    for (int j = 0; j < kRows / kRowStep; ++j) cp_async_16(d0 + j * kRowStep * kDim, s0 + j * kRowStep * kDim, 16u);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kRows / kRowStep; ++j) {
+      const bool valid = r0 + j * kRowStep < rows_valid;
+      cp_async_16(d0 + j * kRowStep * kDim, valid ? s0 + j * kRowStep * kDim : src, valid ? 16u : 0u);
+    }
+  }
+}
+
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows at a
 // 128-byte pitch, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
@@ -125,7 +149,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// 32 consecutive fp32 columns of this thread's lane.
+// 32 consecutive fp32 columns of this thread's lane (issue only: tmem_ld_wait() before use).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t r[32];
   asm volatile(
@@ -137,9 +161,26 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// One key's score from its 64 head dot products (this thread's tensor-memory lane):
+// relu, weight, and four interleaved partial sums (head h goes to sum h & 3) combined as
+// (s0 + s1) + (s2 + s3): four short dependent chains instead of one of 64.  The checker
+// (oracle/oracle_topk.c) sums in the same order.
+__device__ __forceinline__ float score_of_lane(uint32_t taddr, const float* w) {
+  float lo[32], hi[32];
+  tmem_ld32(taddr, lo);
+  tmem_ld32(taddr + 32, hi);
+  tmem_ld_wait();
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int h = 0; h < 32; ++h) acc[h & 3] = fmaf(w[h], fmaxf(lo[h], 0.f), acc[h & 3]);
+#pragma unroll
+  for (int h = 0; h < 32; ++h) acc[h & 3] = fmaf(w[32 + h], fmaxf(hi[h], 0.f), acc[h & 3]);
+  return (acc[0] + acc[1]) + (acc[2] + acc[3]);
 }
 
 struct Shared {
@@ -153,7 +194,7 @@ struct Shared {
   float w[kHeads];
 };
 
-__global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ Shared sh;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
@@ -204,10 +245,7 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
     // ---------------- producers ----------------
     const int pt = tid - kProducerWarp0 * 32;
     const uint8_t* qrow = p.q + static_cast<int64_t>(row) * kQBytes;
-    for (int i = pt; i < kHeads * 8; i += kProducerThreads) {   // 64 heads x 8 chunks of 16 bytes
-      const int r = i >> 3, c = i & 7;
-      cp_async_16(q_s + r * kDim + ((c ^ (r & 7)) << 4), qrow + r * kDim + c * 16, 16u);
-    }
+    copy_rows_swizzled<kHeads>(q_s, qrow, pt, kHeads);
     cp_async_commit();
     cp_async_wait<0>();
     fence_async_proxy();
@@ -221,13 +259,8 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
           (void)mbar_wait(smem_u32(&sh.empty[stage]), static_cast<uint32_t>((i / kStages - 1) & 1), &sh.timed_out);
         }
         const int key0 = (cta + i * n_ctas) * kTileKeys;
-        const uint32_t dst = k_s + stage * kTileBytes;
-        for (int e = pt; e < kTileKeys * 8; e += kProducerThreads) {
-          const int r = e >> 3, c = e & 7;
-          const bool valid = key0 + r < len;
-          const uint8_t* src = krow + static_cast<int64_t>(valid ? key0 + r : 0) * kDim + c * 16;
-          cp_async_16(dst + r * kDim + ((c ^ (r & 7)) << 4), src, valid ? 16u : 0u);   // zero-fill past the end
-        }
+        copy_rows_swizzled<kTileKeys>(k_s + stage * kTileBytes, krow + static_cast<int64_t>(key0) * kDim, pt,
+                                      len - key0);   // zero-fill past the end
       }
       cp_async_commit();   // an empty group keeps the group count in step with i
       const int done = i - (kStages - 1);
@@ -267,14 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1) indexer_logits_kernel(const Param
       (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((i / 2) & 1), &sh.timed_out);
       tc_fence_after();
       const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + buf * kHeads;
-      float s = 0.f;
-      float v[32];
-      tmem_ld32(taddr, v);
-#pragma unroll
-      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[h], fmaxf(v[h], 0.f), s);
-      tmem_ld32(taddr + 32, v);
-#pragma unroll
-      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[32 + h], fmaxf(v[h], 0.f), s);
+      const float s = score_of_lane(taddr, sh.w);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.tempty[buf]));
       const int key = (cta + i * n_ctas) * kTileKeys + key_in_tile;
@@ -468,20 +494,12 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_persistent_kernel(
           }
         }
         const uint8_t* qrow = p.q + static_cast<int64_t>(c.row) * kQBytes;
-        for (int e = pt; e < kHeads * 8; e += kProducerThreads) {
-          const int rr = e >> 3, ch = e & 7;
-          cp_async_16(q_s + qb * kQBytes + rr * kDim + ((ch ^ (rr & 7)) << 4), qrow + rr * kDim + ch * 16, 16u);
-        }
+        copy_rows_swizzled<kHeads>(q_s + qb * kQBytes, qrow, pt, kHeads);
       }
       const uint8_t* krow = p.k + static_cast<int64_t>(c.row) * p.k_row_stride;
       const int key0 = (c.tile0 + c.i) * kTileKeys;
-      const uint32_t dst = k_s + stage * kTileBytes;
-      for (int e = pt; e < kTileKeys * 8; e += kProducerThreads) {
-        const int rr = e >> 3, ch = e & 7;
-        const bool valid = key0 + rr < c.len;
-        const uint8_t* src = krow + static_cast<int64_t>(valid ? key0 + rr : 0) * kDim + ch * 16;
-        cp_async_16(dst + rr * kDim + ((ch ^ (rr & 7)) << 4), src, valid ? 16u : 0u);
-      }
+      copy_rows_swizzled<kTileKeys>(k_s + stage * kTileBytes, krow + static_cast<int64_t>(key0) * kDim, pt,
+                                    c.len - key0);
       cp_async_commit();
       lag += 1;
       more = cursor_next(c, p, sh.prefix, B, total_units, stride);
@@ -538,14 +556,7 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_persistent_kernel(
       (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((c.t / 2) & 1), &sh.timed_out);
       tc_fence_after();
       const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + buf * kHeads;
-      float s = 0.f;
-      float v[32];
-      tmem_ld32(taddr, v);
-#pragma unroll
-      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[h], fmaxf(v[h], 0.f), s);
-      tmem_ld32(taddr + 32, v);
-#pragma unroll
-      for (int h = 0; h < 32; ++h) s = fmaf(sh.w[32 + h], fmaxf(v[h], 0.f), s);
+      const float s = score_of_lane(taddr, sh.w);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.tempty[buf]));
       const int key = (c.tile0 + c.i) * kTileKeys + key_in_tile;
@@ -625,8 +636,10 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   p.L_width = L_width;
   p.tiles_per_cta = 0;
   p.status = status;
-  if (ctas_per_row <= 0 && B <= ffl::kMaxRowsPersistent) {
-    // Automatic: the persistent kernel, two CTAs per SM, units of 8 tiles dealt out round robin.
+  if (ctas_per_row < 0) {
+    // The persistent kernel, two CTAs per SM, units of 8 tiles dealt out round robin.  Measured a few
+    // per cent slower than shares of 32 tiles per CTA (below), which is therefore the default.
+    if (B > ffl::kMaxRowsPersistent) return fail(-6, "the persistent kernel takes at most 1024 rows");
     int sms = 148;
     (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     const int64_t max_units = static_cast<int64_t>(B) * ((tiles + ffl::kUnitTiles - 1) / ffl::kUnitTiles);
@@ -637,9 +650,9 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return 0;
   }
-  // A fixed number of CTAs per row (or a batch too large for the persistent kernel's row table):
-  // shares of about 32 tiles (512 KiB of K), but at least about four CTAs per SM in total when
-  // every row is full, so that small batches still fill the device.
+  // Default (ctas_per_row == 0): every row is cut into shares of about 32 tiles (512 KiB of K), but
+  // into at least so many that the batch has about four CTAs per SM when every row is full, so that
+  // small batches still fill the device.  ctas_per_row > 0 fixes the number of CTAs of a full row.
   int per_row = ctas_per_row;
   int tiles_per_cta = 32;
   if (per_row <= 0) {

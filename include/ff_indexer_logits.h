@@ -8,7 +8,8 @@
  *     scores[b, j] = sum over h < 64 of  w[b, h] * relu( q[b, h, :] . k[b, j, :] )
  *
  * with head_dim 128, q and k in fp8 e4m3 (one byte per element), products and
- * sums in fp32, heads summed in index order with fused multiply-adds.
+ * sums in fp32; heads summed with fused multiply-adds into four interleaved partial sums
+ * (head h into sum h & 3) that are combined as (s0 + s1) + (s2 + s3).
  * Positions j >= lengths[b] inside a processed 128-key tile receive -inf;
  * tiles that start at or beyond lengths[b] are left untouched.
  *
@@ -33,7 +34,9 @@ extern "C" {
 /* q_e4m3: [B, 64, 128] bytes, contiguous, 16-byte aligned.
  * k_e4m3: key j of row b at k_e4m3 + b * k_row_stride_bytes + j * 128 (16-byte aligned stride).
  * w: [B, 64] float32.  lengths: [B] int32.  scores: [B, score_stride] float32, score_stride >= L_width.
- * ctas_per_row: 0 = automatic (about two waves of CTAs over the batch). */
+ * ctas_per_row: 0 = automatic (shares of about 32 tiles of 128 keys per CTA, sized from each row's
+ * length on the device); > 0 = that many CTAs for a full row; < 0 = the persistent variant (two CTAs
+ * per SM walk units of 8 tiles round robin; at most 1024 rows). */
 int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_row_stride_bytes,
                              const float* w, const int32_t* lengths, float* scores,
                              int64_t score_stride, int32_t B, int32_t L_width, int32_t ctas_per_row,

@@ -127,7 +127,8 @@ uint32_t oracle_key_of_bits(uint32_t u) { return key_of_bits(u); }
  * The dot product is summed in double, which is exact for 128 products of such values,
  * and `*inexact` counts the dot products that are not representable in float (none
  * for the seeded workloads: then every fp32 summation order gives this same value).
- * The heads are summed in index order with fmaf, as the kernel does.  The operation
+ * The heads are summed with fmaf into four interleaved partial sums that are then added
+ * pairwise, as the kernel does.  The operation
  * is the one the reference's README names for its indexer (README.md:28). */
 #include <math.h>
 int oracle_indexer_logits(const float* q, const float* k, const float* w, int64_t n_keys,
@@ -135,16 +136,16 @@ int oracle_indexer_logits(const float* q, const float* k, const float* w, int64_
   int64_t bad = 0;
   for (int64_t j = 0; j < n_keys; ++j) {
     const float* kj = k + j * 128;
-    float s = 0.0f;
+    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};   /* head h goes to partial sum h & 3, as in the kernel */
     for (int h = 0; h < 64; ++h) {
       const float* qh = q + h * 128;
       double acc = 0.0;
       for (int d = 0; d < 128; ++d) acc += (double)qh[d] * (double)kj[d];
       const float dot = (float)acc;
       if ((double)dot != acc) ++bad;
-      s = fmaf(w[h], dot > 0.0f ? dot : 0.0f, s);
+      part[h & 3] = fmaf(w[h], dot > 0.0f ? dot : 0.0f, part[h & 3]);
     }
-    out[j] = s;
+    out[j] = (part[0] + part[1]) + (part[2] + part[3]);
   }
   if (inexact) *inexact = bad;
   return 0;

@@ -53,8 +53,8 @@ def _make(B, L, seed, device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,L,lens,ctas", [(1, 128, [128], 1), (2, 1000, [1000, 37], 0), (3, 5000, [5000, 4097, 129], 3),
-                                           (2, 20000, [20000, 1], 0), (5, 3000, [3000, 0, 129, 2999, 1024], 0),
-                                           (70, 2100, [2100 - 29 * i for i in range(70)], 0)])
+                                           (2, 20000, [20000, 1], -1), (5, 3000, [3000, 0, 129, 2999, 1024], -1), (5, 3000, [3000, 0, 129, 2999, 1024], 0),
+                                           (70, 2100, [2100 - 29 * i for i in range(70)], -1)])
 def test_logits_are_bit_exact_against_the_oracle(oracle, B, L, lens, ctas):
     from flash_float_jit_kernels_b200.indexer_logits import indexer_logits_fp8
     dev = torch.device("cuda:0")
