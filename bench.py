@@ -579,6 +579,26 @@ def run_profile_case(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     name = args.profile_case
+    if name == "logits":
+        # the indexer-logit producer on a ragged batch of 32 rows x 65,536 keys (256 MiB of fp8 K, larger than L2)
+        from flash_float_jit_kernels_b200.indexer_logits import indexer_logits_fp8
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        B, Lm = 32, 65536
+        f8 = torch.float8_e4m3fn
+        q = (torch.randn((B, 64, 128), generator=g, device=dev) / 4).to(f8)
+        w = torch.rand((B, 64), generator=g, device=dev)
+        kc = torch.empty((B, Lm, 128), dtype=f8, device=dev)
+        for b in range(B):
+            kc[b] = (torch.randn((Lm, 128), generator=g, device=dev) / 4).to(f8)
+        lens = torch.randint(4096, Lm + 1, (B,), generator=g, device=dev, dtype=torch.int32)
+        sc = torch.full((B, Lm), float("-inf"), device=dev)
+        for _ in range(max(args.warmup, 1) + args.steps):
+            indexer_logits_fp8(q, kc, w, lens, out=sc)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case": name, "launches": max(args.warmup, 1) + args.steps,
+                          "k_bytes_per_launch": 128 * int(lens.sum())}))
+        return
     n_rot = 40   # 40 x 4 MiB = 160 MiB > L2 for the 1M-column cases
     if name == "headline":
         rows = make_rows(n_rot, L_SHARD, dev, seed=1).view(n_rot, 1, L_SHARD)
@@ -614,7 +634,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch the steps eagerly instead of replaying a graph")
     ap.add_argument("--exchange", default="auto", choices=["auto", "p2p", "nccl"], help="N > 1: candidate exchange")
-    ap.add_argument("--profile-case", default=None, choices=["headline", "unique16k", "b64"],
+    ap.add_argument("--profile-case", default=None, choices=["headline", "unique16k", "b64", "logits"],
                     help="run a few eager launches of one configuration and exit (for ncu)")
     args = ap.parse_args()
     if args.profile_case:
