@@ -7,7 +7,7 @@
 // peer's slot as it ranks them, one 8-byte store per entry.  An 8-byte aligned
 // store arrives whole, so the step number inside the entry is its own "valid"
 // mark: the receiver polls an entry until it carries the current step (bounded
-// wait).  No fence, no flag, no collective library call, no multicast; the
+// wait).  No fence, no flag, no collective library call; the
 // receiver reads local memory only.
 // The reference has no multi-GPU path; semantics follow fast_topk_v3
 // (jit_kernel/topk_indexer.py:109) on the unsharded row.

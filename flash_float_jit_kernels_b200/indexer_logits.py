@@ -92,3 +92,18 @@ def indexer_logits_fp8(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, length
     if rc > 0:
         raise RuntimeError(f"indexer_logits_fp8: {lib.ff_indexer_last_error_string().decode()}")
     return out
+
+
+def indexer_topk(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, lengths: torch.Tensor, topk: int, *,
+                 scores: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                 threshold_hint: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step of the indexer: logits from the fp8 K cache, then their top-k.
+
+    Two launches on the current stream (producer, select), no host synchronisation; pass
+    ``scores`` (B, L) float32, ``out`` (B, topk) int32 and, to carry threshold guesses from
+    step to step, ``threshold_hint`` (see ``fast_topk_v3``) to keep the step allocation-free.
+    Returns the (B, topk) int32 indices.
+    """
+    from .topk_indexer import fast_topk_v3
+    scores = indexer_logits_fp8(q, k, w, lengths, out=scores, status=status)
+    return fast_topk_v3(scores, lengths, topk, out=out, status=status, threshold_hint=threshold_hint)

@@ -92,3 +92,26 @@ def test_logits_feed_the_indexer(oracle):
         n = int(lengths[b])
         exp_scores[b, :n] = oracle.indexer_logits(q[b].float().numpy(), k[b, :n].float().numpy(), w[b].numpy())[0]
     assert np.array_equal(idx.cpu().numpy(), oracle.topk_c(exp_scores, lengths.numpy(), k_top))
+
+
+@pytest.mark.gpu
+def test_decode_step_with_threshold_guesses(oracle):
+    """indexer_topk over a few steps of a growing K cache, guesses carried along: exact every step."""
+    from flash_float_jit_kernels_b200 import new_threshold_hint
+    from flash_float_jit_kernels_b200.indexer_logits import indexer_topk
+    dev = torch.device("cuda:0")
+    B, L, k_top = 2, 12000, 256
+    q, k, w = _make(B, L, 21, dev)
+    qd, kd, wd = q.to(dev), k.to(dev), w.to(dev)
+    scores = torch.full((B, L), float("-inf"), device=dev)
+    out = torch.empty((B, k_top), dtype=torch.int32, device=dev)
+    hint = new_threshold_hint(B, dev)
+    for step in range(3):
+        lengths = torch.tensor([11000 + 300 * step, 7000 + 100 * step], dtype=torch.int32)
+        indexer_topk(qd, kd, wd, lengths.to(dev), k_top, scores=scores, out=out, threshold_hint=hint)
+        torch.cuda.synchronize()
+        exp_scores = np.full((B, L), -np.inf, dtype=np.float32)
+        for b in range(B):
+            n = int(lengths[b])
+            exp_scores[b, :n] = oracle.indexer_logits(q[b].float().numpy(), k[b, :n].float().numpy(), w[b].numpy())[0]
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(exp_scores, lengths.numpy(), k_top)), step

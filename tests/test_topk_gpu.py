@@ -349,3 +349,25 @@ def test_threshold_hint_short_rows_and_special_values(oracle):
         torch.cuda.synchronize()
         assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), step
     assert torch.isnan(hint[1])          # short row: no guess
+
+
+@pytest.mark.parametrize("k", [1, 7, 2048])
+def test_threshold_hint_edge_shapes(oracle, k):
+    """Guesses with windows (row_starts), k = 1, rows barely longer than k, heavy ties and outliers."""
+    from flash_float_jit_kernels_b200 import fast_topk_v3, new_threshold_hint
+    dev = torch.device("cuda:0")
+    B, L = 5, 6000
+    g = torch.Generator().manual_seed(900 + k)
+    lengths = torch.tensor([L - 100, max(k + 1, 50), 4097, L - 2048, 3000], dtype=torch.int32)
+    starts = torch.tensor([100, 0, 3, 2048, 1], dtype=torch.int32)
+    hint = new_threshold_hint(B, dev)
+    for step in range(4):
+        s = torch.randn((B, L), generator=g)
+        s[2] = torch.round(s[2] * 2) / 2            # a few distinct values: ties far beyond 4096 per value
+        s[3, ::97] += 50.0                          # far outliers
+        if step == 2:
+            s[4] = 0.25                             # constant row: the guess cannot separate anything
+        out = fast_topk_v3(s.to(dev), lengths.to(dev), k, starts.to(dev), threshold_hint=hint)
+        torch.cuda.synchronize()
+        exp = oracle.topk_c(s.numpy(), lengths.numpy(), k, starts.numpy())
+        assert np.array_equal(out.cpu().numpy(), exp), step
