@@ -212,6 +212,7 @@ def bench_single(args):
     for _ in range(3):
         e2e_step()
     torch.cuda.synchronize()
+    e2e_mode = "eager calls on the current stream"   # (one CUDA graph replay per step measured slower: 262 us)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(Ke):
@@ -239,7 +240,7 @@ def bench_single(args):
                      "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 5)},
         "cpu_baseline": cpu,
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": 4 * L, "d2h_bytes_per_step": 4 * k,
-                "steps": Ke},
+                "steps": Ke, "mode": e2e_mode},
         "gpu_launches": int(launches_per_replay),
         "clocks": clocks,
         "extra": extra,
