@@ -48,12 +48,12 @@ def _stream_ptr(device: torch.device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
-def _workspace(lib, device: torch.device, B: int, L: int, k: int):
+def _workspace(lib, device: torch.device, B: int, L: int, k: int, stream: Optional[int] = None):
     """Per-(device, stream) scratch, grown on demand and zero-filled once."""
     need = int(lib.ff_topk_workspace_bytes(B, L, k))
     if need == 0:
         return None, 0
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream if stream is None else stream)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(need, dtype=torch.uint8, device=device)
@@ -126,21 +126,30 @@ def fast_topk_v3(
                  and out.device == score.device, "out must be a contiguous (B, topk) int32 tensor")
     if B == 0:
         return out
-    ws, ws_bytes = _workspace(lib, score.device, B, L, topk)
+    dev = score.device
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws, ws_bytes = _workspace(lib, dev, B, L, topk, stream)
     row_stride = score.stride(0) if B > 1 else max(score.stride(0), L)
-    with torch.cuda.device(score.device):
+    if threshold_hint is not None:
+        _require(threshold_hint.shape == (B,) and threshold_hint.dtype == torch.float32
+                 and threshold_hint.is_contiguous() and threshold_hint.device == dev,
+                 "threshold_hint must be a contiguous (B) float32 tensor on score's device")
+
+    def call():
         if threshold_hint is None:
-            rc = lib.ff_topk_launch(
+            return lib.ff_topk_launch(
                 score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
-                _ptr(ws), ws_bytes, _ptr(status), _stream_ptr(score.device))
-        else:
-            _require(threshold_hint.shape == (B,) and threshold_hint.dtype == torch.float32
-                     and threshold_hint.is_contiguous() and threshold_hint.device == score.device,
-                     "threshold_hint must be a contiguous (B) float32 tensor on score's device")
-            rc = lib.ff_topk_launch_hinted(
-                score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
-                threshold_hint.data_ptr(), threshold_hint.data_ptr(), _ptr(ws), ws_bytes, _ptr(status),
-                _stream_ptr(score.device))
+                _ptr(ws), ws_bytes, _ptr(status), stream)
+        return lib.ff_topk_launch_hinted(
+            score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
+            threshold_hint.data_ptr(), threshold_hint.data_ptr(), _ptr(ws), ws_bytes, _ptr(status), stream)
+
+    # the library launches on the current device: switch only when score lives elsewhere
+    if torch.cuda.current_device() == dev.index:
+        rc = call()
+    else:
+        with torch.cuda.device(dev):
+            rc = call()
     _lib.check(rc, "fast_topk_v3")
     return out
 
