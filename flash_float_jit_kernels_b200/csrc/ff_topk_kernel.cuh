@@ -1273,6 +1273,58 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   if (my_share == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
     atomicOr(p.status, 1);
 
+  // ---- finish, many CTAs on the row: rank by direct counting ------------------
+  // With n CTAs on the row, CTA s owns the survivors i = s, s + n, ...  When that is at most 32
+  // of them (rows split over many clusters), 16 lanes per owned survivor simply count the
+  // survivors above it in this CTA's copy of the list (T / 16 compares per lane): no
+  // histogram, scan or scatter, one pass and one barrier-free reduction.
+  if (T <= 32 * n_share) {
+    const int l16 = tid & 15;
+    const int i = my_share + (tid >> 4) * n_share;
+    const bool valid = i < T;
+    const uint64_t c = valid ? sortbuf[i] : ~0ull;
+    int cnt = 0;
+#pragma unroll 4
+    for (int q = l16; q < T; q += 16) cnt += sortbuf[q] > c ? 1 : 0;
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, 8);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
+    cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
+    if (valid && l16 == 0 && cnt < k)
+      emit<kPush>(p, push, row, cnt, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (kHinted && !HAS_MAP && p.hint_out != nullptr) {
+      // Next call's guess: the score of rank min(T, 3k/2) - 1, written by its owner.  With fewer
+      // than 3k/2 survivors that is the smallest one; its owner then extrapolates linearly below
+      // it with the owned survivor whose rank is nearest to T/2 (ranks of the others are not known here).
+      uint32_t* mid = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [32][3]: |rank - T/2|, value bits, rank
+      if (l16 == 0) {
+        mid[3 * (tid >> 4)] = valid ? static_cast<uint32_t>(abs(cnt - (T >> 1))) : 0x7fffffffu;
+        mid[3 * (tid >> 4) + 1] = bits_of_key(comp_key(c));
+        mid[3 * (tid >> 4) + 2] = static_cast<uint32_t>(cnt);
+      }
+      __syncthreads();
+      if (valid && l16 == 0 && cnt == hint_rank) {
+        const float va = __uint_as_float(bits_of_key(comp_key(c)));
+        float guess = va;
+        const int want = k + (k >> 1);
+        if (T < want) {
+          int best = 0;
+          for (int g = 1; g < 32; ++g)
+            if (mid[3 * g] < mid[3 * best]) best = g;
+          const float vm = __uint_as_float(mid[3 * best + 1]);
+          const int gap = hint_rank - static_cast<int>(mid[3 * best + 2]);   // ranks between the two
+          if (mid[3 * best] < static_cast<uint32_t>(T >> 2) && gap > 0) {
+            const float lower = va - (vm - va) * (static_cast<float>(want - T) / static_cast<float>(gap));
+            if (lower == lower && fabsf(lower) <= 3.0e38f) guess = lower;
+          }
+        }
+        p.hint_out[row] = guess;
+      }
+    }
+    FF_TRACE(p, 25);
+    return;
+  }
+
   // ---- finish: rank the T survivors and write the first k ------------------
   // A counting sort on an adaptive linear digit: bin = (comp - floor) >> shift
   // with shift chosen so the survivors' composite range spans <= 4096 bins (any
