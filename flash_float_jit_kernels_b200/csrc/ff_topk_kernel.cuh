@@ -1275,35 +1275,54 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 
   // ---- finish, many CTAs on the row: rank by direct counting ------------------
   // With n CTAs on the row, CTA s owns the survivors i = s, s + n, ...  When that is at most 32
-  // of them (rows split over many clusters), 16 lanes per owned survivor simply count the
-  // survivors above it in this CTA's copy of the list (T / 16 compares per lane): no
-  // histogram, scan or scatter, one pass and one barrier-free reduction.
+  // of them (rows split over many clusters), the CTA's threads simply count the
+  // survivors above it in this CTA's copy of the list: no histogram, scan or scatter.
   if (T <= 32 * n_share) {
-    const int l16 = tid & 15;
-    const int i = my_share + (tid >> 4) * n_share;
-    const bool valid = i < T;
+    // Register blocking: a group of 64 lanes (two warps) holds four owned survivors per lane and
+    // streams the list once for all four, so shared memory is read half as often as it is compared.
+    uint32_t* cnt_arr = reinterpret_cast<uint32_t*>(smem + kSmemRing + 1024);   // [32] ranks
+    if (tid < 32) cnt_arr[tid] = 0u;
+    const int grp = tid >> 6, l64 = tid & 63;
+    uint64_t own[4];
+    int part[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int idx = my_share + (grp * 4 + e) * n_share;
+      own[e] = idx < T ? sortbuf[idx] : ~0ull;
+      part[e] = 0;
+    }
+    __syncthreads();
+#pragma unroll 2
+    for (int q = l64; q < T; q += 64) {
+      const uint64_t o = sortbuf[q];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) part[e] += o > own[e] ? 1 : 0;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int v = __reduce_add_sync(0xffffffffu, part[e]);
+      if ((tid & 31) == 0 && v != 0) atomicAdd(&cnt_arr[grp * 4 + e], static_cast<uint32_t>(v));
+    }
+    __syncthreads();
+    // threads 0..31 finish one owned survivor each
+    const int i = my_share + tid * n_share;
+    const bool valid = tid < 32 && i < T;
     const uint64_t c = valid ? sortbuf[i] : ~0ull;
-    int cnt = 0;
-#pragma unroll 4
-    for (int q = l16; q < T; q += 16) cnt += sortbuf[q] > c ? 1 : 0;
-    cnt += __shfl_xor_sync(0xffffffffu, cnt, 8);
-    cnt += __shfl_xor_sync(0xffffffffu, cnt, 4);
-    cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
-    cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
-    if (valid && l16 == 0 && cnt < k)
+    const int cnt = valid ? static_cast<int>(cnt_arr[tid]) : 0;
+    if (valid && cnt < k)
       emit<kPush>(p, push, row, cnt, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
     if (kHinted && !HAS_MAP && p.hint_out != nullptr) {
       // Next call's guess: the score of rank min(T, 3k/2) - 1, written by its owner.  With fewer
       // than 3k/2 survivors that is the smallest one; its owner then extrapolates linearly below
       // it with the owned survivor whose rank is nearest to T/2 (ranks of the others are not known here).
       uint32_t* mid = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [32][3]: |rank - T/2|, value bits, rank
-      if (l16 == 0) {
-        mid[3 * (tid >> 4)] = valid ? static_cast<uint32_t>(abs(cnt - (T >> 1))) : 0x7fffffffu;
-        mid[3 * (tid >> 4) + 1] = bits_of_key(comp_key(c));
-        mid[3 * (tid >> 4) + 2] = static_cast<uint32_t>(cnt);
+      if (tid < 32) {
+        mid[3 * tid] = valid ? static_cast<uint32_t>(abs(cnt - (T >> 1))) : 0x7fffffffu;
+        mid[3 * tid + 1] = bits_of_key(comp_key(c));
+        mid[3 * tid + 2] = static_cast<uint32_t>(cnt);
       }
       __syncthreads();
-      if (valid && l16 == 0 && cnt == hint_rank) {
+      if (valid && cnt == hint_rank) {
         const float va = __uint_as_float(bits_of_key(comp_key(c)));
         float guess = va;
         const int want = k + (k >> 1);
