@@ -481,14 +481,17 @@ __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_un
 //   [0, 6)   arrivals at the histogram barrier of digit level 0..5
 //   [6]      arrivals at the survivor barrier      [7] CTAs that are done
 //   [8]      survivors appended so far
-//   [9]      arrivals at the barrier of a hinted attempt   [10] survivors it appended
+//   [10,11]  hinted attempt: one 64-bit word, low half survivors appended, high half CTAs that have reserved
 //   [64, 320) first digit level only: the row's histogram summed in groups of 32 bins
 //   [320, 320 + 6 * 8192)        one 8192-bin global histogram per digit level
-//   [320 + 6 * 8192, + 2 * 4096) survivor list (4096 x 64-bit composites)
+//   [320 + 6 * 8192, + 2 * 4096) survivor list (4096 x 64-bit composites), then a second one for a hinted
+//                                attempt.  Both are zero between launches: an entry is valid once it is
+//                                non-zero (no composite is zero), so readers need no barrier after the writes
 constexpr int kWsCoarseWord = 64;            // 256 coarse bins (sums of 32 first-level bins) of the row
 constexpr int kWsHeaderWords = 64 + 256;
 constexpr int kWsHistWords = kNumLevels * kMaxBins;
-constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kSortCap;
+constexpr int kWsListWords = 2 * kSortCap;     // one survivor list (64-bit composites)
+constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kWsListWords;   // + the list of a hinted attempt
 constexpr int kSpinLimit = 1 << 21;   // bounded polling of a row barrier (about a second)
 
 // All `expected` CTAs of a row meet here (they are co-resident: cooperative
@@ -512,6 +515,34 @@ __device__ __forceinline__ bool row_barrier(uint32_t* counter, uint32_t expected
   }
   __syncthreads();
   return *flag != 0;
+}
+
+// Copies the first n entries of a global survivor list into shared memory.  The list is zero
+// between launches and no composite is zero, so an entry is valid as soon as it is non-zero:
+// each thread polls its own entries (bounded), and no barrier or fence follows the writers.
+__device__ __forceinline__ bool load_list_validated(const uint64_t* glist, int n, uint64_t* dst) {
+  // all of a thread's entries are requested before the first one is looked at (the list has at
+  // most kSortCap entries: kSortCap / kThreads per thread); only missing ones are polled again
+  constexpr int kPer = kSortCap / kThreads;
+  unsigned long long v[kPer];
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int i = static_cast<int>(threadIdx.x) + j * kThreads;
+    v[j] = 1ull;
+    if (i < n) asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v[j]) : "l"(glist + i));
+  }
+  bool ok = true;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int i = static_cast<int>(threadIdx.x) + j * kThreads;
+    if (i < n) {
+      for (int spin = 0; v[j] == 0ull && spin < kSpinLimit; ++spin)
+        asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v[j]) : "l"(glist + i) : "memory");
+      if (v[j] == 0ull) ok = false;
+      dst[i] = v[j];
+    }
+  }
+  return ok;
 }
 
 // Cluster-wide histogram merge (reduce-scatter over distributed shared memory)
@@ -975,12 +1006,20 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // list is all-gathered into EVERY peer over DSMEM, so each CTA ends up with the full list and
   // can take a share of the finishing work without further exchange; rows split over clusters
   // keep it in global scratch (count word `gcount`).
-  auto gather_stage = [&](int n_true, uint32_t* gcount) {
+  auto gather_stage = [&](int n_true, bool hinted_attempt) {
     const int n_stage = min(n_true, kSortCap);
-    if (n_true > 0 && G > 1) {
-      if (tid == 0) sh.push_base = static_cast<int>(atomicAdd(gcount, static_cast<uint32_t>(n_true)));
+    if (G > 1 && (n_true > 0 || hinted_attempt)) {
+      if (tid == 0) {
+        if (hinted_attempt) {   // survivors and "this CTA has reserved" in one atomic: readers see both or neither
+          const unsigned long long old = atomicAdd(reinterpret_cast<unsigned long long*>(ws + 10),
+                                                   static_cast<unsigned long long>(n_true) | (1ull << 32));
+          sh.push_base = static_cast<int>(static_cast<uint32_t>(old));
+        } else {
+          sh.push_base = static_cast<int>(atomicAdd(ws + 8, static_cast<uint32_t>(n_true)));
+        }
+      }
       __syncthreads();
-      uint64_t* gsurv = reinterpret_cast<uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
+      uint64_t* gsurv = reinterpret_cast<uint64_t*>(ws + kWsHeaderWords + kWsHistWords + (hinted_attempt ? kWsListWords : 0));
       const int base = sh.push_base;
       for (int i = tid; i < n_stage; i += kThreads) {
         if (base + i < kSortCap) gsurv[base + i] = stage[i];
@@ -1018,6 +1057,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // finished from them directly.  Otherwise (a miss, reported as FF_STATUS_HINT_MISSED) the
   // row starts over on the histogram path below; the result is exact either way.
   bool hinted_done = false;
+  int hinted_total = 0;     // entries a hinted attempt left in its global list (rows split over clusters)
   float hint = 0.f;
   bool use_hint = false;
   if (kHinted && !HAS_MAP && p.hint_in != nullptr) {
@@ -1039,25 +1079,38 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     }
     __syncthreads();
     FF_TRACE(p, 3);
-    gather_stage(sh.stage_count, G > 1 ? ws + 10 : nullptr);
+    gather_stage(sh.stage_count, true);
     FF_TRACE(p, 4);
     int total;
     if (G > 1) {
-      if (!row_barrier(ws + 9, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
-      total = static_cast<int>(__ldcg(ws + 10));
+      // every CTA of the row has reserved when the word's high half reaches n_share; its low half is then the total
+      if (tid == 0) {
+        unsigned long long v = 0ull;
+        int spin = 0;
+        for (; spin < kSpinLimit; ++spin) {
+          asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ws + 10) : "memory");
+          if (static_cast<uint32_t>(v >> 32) >= static_cast<uint32_t>(n_share)) break;
+        }
+        sh.flag = spin < kSpinLimit ? 1 : 0;
+        sh.push_base = static_cast<int>(static_cast<uint32_t>(v));
+      }
+      __syncthreads();
+      if (!sh.flag) ts.timed_out = true;
+      total = sh.push_base;
     } else if (C > 1) {
       cluster.sync();
       total = static_cast<int>(dsmem_ld_u32(dsmem_addr(smem_addr(&sh.sort_count), 0)));
     } else {
       total = sh.sort_count;
     }
+    hinted_total = G > 1 ? min(total, kSortCap) : 0;
     if (total >= k && total <= kSortCap) {
       hinted_done = true;
       expected_total = total;
       floor_comp = static_cast<uint64_t>(key_of(hint)) << 32;
       if (G > 1) {
-        const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
-        for (int i = tid; i < total; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
+        const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords + kWsListWords);
+        if (!load_list_validated(gsurv, total, sortbuf)) ts.timed_out = true;
         if (my_share == 0 && tid == 0) sh.sort_count = total;
       }
     } else {
@@ -1217,7 +1270,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     __syncthreads();
     FF_TRACE(p, 3 + 3 * level);
 
-    gather_stage(min(sh.stage_count, kSortCap), G > 1 ? ws + 8 : nullptr);
+    gather_stage(min(sh.stage_count, kSortCap), false);
     FF_TRACE(p, 4 + 3 * level);
     if (tid == 0) sh.stage_count = 0;
     if (ctx.compact && !src_is_cand) {
@@ -1235,12 +1288,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   }   // !hinted_done
 
   if (G > 1) {
+    const int n_load = (!hinted_done && ok) ? min(expected_total, kSortCap) : 0;
     if (!hinted_done) {
-      if (!row_barrier(ws + 6, static_cast<uint32_t>(n_share), &sh.flag)) ts.timed_out = true;
+      // no barrier: the histogram told every CTA how many survivors to expect, and entries validate themselves
       const uint64_t* gsurv = reinterpret_cast<const uint64_t*>(ws + kWsHeaderWords + kWsHistWords);
-      const int n_load = ok ? min(expected_total, kSortCap) : 0;
-      for (int i = tid; i < n_load; i += kThreads) sortbuf[i] = __ldcg(&gsurv[i]);
-      if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));
+      if (!load_list_validated(gsurv, n_load, sortbuf)) ts.timed_out = true;
+      __syncthreads();
+      if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));   // all of them have been reserved by now
     }
     __syncthreads();
     // Last use of the scratch: the CTA that counts in last zeroes it for the next launch.
@@ -1251,6 +1305,11 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     __syncthreads();
     if (sh.flag) {
       for (int i = tid; i < kWsHeaderWords + levels_used * kMaxBins; i += kThreads) ws[i] = 0u;
+      // the lists must read as empty for the next launch (a failed select may have left any number of entries)
+      uint32_t* lists = ws + kWsHeaderWords + kWsHistWords;
+      const int n_plain = hinted_done ? 0 : (ok ? n_load : kSortCap);
+      for (int i = tid; i < 2 * n_plain; i += kThreads) lists[i] = 0u;
+      for (int i = tid; i < 2 * hinted_total; i += kThreads) lists[kWsListWords + i] = 0u;
     }
   } else if (C > 1) {
     if (!hinted_done) cluster.sync();   // every survivor has landed in every CTA's list

@@ -91,7 +91,7 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
  * still works but handles a long row with a single cluster; this entry point
  * keeps the fast path (a long row split over several clusters) by using scratch
  * built into the library: a zero-initialised __device__ array of
- * FF_TOPK_STATIC_MAX_ROWS * 230,656 bytes (about 901 KiB) that every GPU
+ * FF_TOPK_STATIC_MAX_ROWS * 263,424 bytes (about 1029 KiB) that every GPU
  * loading the library holds until the process exits.
  *   - B > FF_TOPK_STATIC_MAX_ROWS is rejected with FF_ERR_TOO_LARGE.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine; it
