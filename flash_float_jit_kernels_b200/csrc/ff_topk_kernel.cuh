@@ -553,7 +553,10 @@ __device__ __forceinline__ bool load_list_validated(const uint64_t* glist, int n
 __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C, int rank,
                                                uint32_t* hist, uint32_t* merged, int nbins, int r,
                                                bool raw0, ClusterShared& sh, const TopkParams& p, bool tr,
-                                               int G, uint32_t* ws, int level, bool& timed_out) {
+                                               int G, uint32_t* ws, int level, bool& timed_out,
+                                               int counted = -1) {
+  // counted: how many elements the histograms of the whole row hold at this level (first level: the
+  // row's length), or -1 if not known
   const int tid = threadIdx.x;
   int slice_n = nbins / C;
   int slice_base = rank * slice_n;
@@ -636,6 +639,13 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
     // first level: also a coarse view (groups of 32 bins), so that after the barrier a CTA reads
     // 256 + 32 words instead of the whole histogram
     const bool two_step = level == 0 && nbins == kMaxBins;
+    const bool self_counting = two_step && counted >= 0;
+    if (self_counting) {
+      // No arrival counter: every CTA orders its fine-bin additions before its coarse sums, and the
+      // coarse sums of the row add up to `counted` exactly when every CTA's have landed.
+      __threadfence();
+      __syncthreads();
+    }
     if (two_step) {
       const int lane = tid & 31;
       for (int g = tid >> 5; g < slice_n / 32; g += kWarps) {
@@ -643,11 +653,26 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
         if (lane == 0 && sum != 0u) atomicAdd(ws + kWsCoarseWord + slice_base / 32 + g, sum);
       }
     }
-    if (!row_barrier(ws + level, static_cast<uint32_t>(G * C), &sh.flag)) timed_out = true;
+    if (!self_counting) {
+      if (!row_barrier(ws + level, static_cast<uint32_t>(G * C), &sh.flag)) timed_out = true;
+    }
     if (two_step) {
-      const int val = tid < 256 ? static_cast<int>(__ldcg(ws + kWsCoarseWord + tid)) : 0;
-      int total;
-      const int excl = block_suffix_exclusive(val, sh.warp_tot, total);
+      int val = 0, total = 0, excl = 0;
+      if (self_counting) {
+        // the poll is the coarse scan itself: read, sum, repeat until the sum is complete (bounded)
+        bool complete = false;
+        for (int spin = 0; spin < (kSpinLimit >> 6) && !complete; ++spin) {
+          uint32_t w = 0u;
+          if (tid < 256) asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(w) : "l"(ws + kWsCoarseWord + tid) : "memory");
+          val = static_cast<int>(w);
+          excl = block_suffix_exclusive(val, sh.warp_tot, total);
+          complete = total == counted;
+        }
+        if (!complete) timed_out = true;
+      } else {
+        val = tid < 256 ? static_cast<int>(__ldcg(ws + kWsCoarseWord + tid)) : 0;
+        excl = block_suffix_exclusive(val, sh.warp_tot, total);
+      }
       if (tid < 256 && excl < r && r <= excl + val) {
         sh.res[3] = tid;
         sh.res[1] = excl;
@@ -1160,7 +1185,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       merge_two_step(cluster, C, hist, merged, r, sh, p);
     } else {
       merge_and_scan(cluster, C, rank, hist, merged, 1 << bits, r, raw0, sh, p, level == 0, G, ws, level,
-                     ts.timed_out);
+                     ts.timed_out, (level == 0 && !HAS_MAP) ? len : -1);
     }
     levels_used = level + 1;
     FF_TRACE(p, 2 + 3 * level);
