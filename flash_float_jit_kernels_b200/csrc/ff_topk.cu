@@ -150,9 +150,15 @@ int choose_cluster(int device, int32_t B, int64_t L_width, int32_t k) {
 // all SMs sweep them; that needs the caller's zero-filled workspace and a
 // cooperative launch (all CTAs of a row wait for each other through global
 // memory).  Returns the number of clusters per row and may lower `cluster`.
-constexpr int64_t kGroupMinWidth = 786432;
+// Measured on B200 (B = 1, k = 2048, clusters of 8): with 15 or more clusters a split row beats one
+// cluster of 16 from 128 Ki columns up (15.9 against 16.2 us; 16.8 against 20.3 us at 512 Ki), and
+// with a threshold guess from 64 Ki up (10.1 against 12.5 us); with only 4 clusters it loses below
+// 768 Ki columns.  So shorter rows are split only if at least 8 clusters are free for each.
+constexpr int64_t kGroupMinWidth = 131072;
+constexpr int64_t kGroupMinWidthHinted = 65536;
+constexpr int64_t kGroupAlwaysWidth = 786432;
 constexpr int kGroupCluster = 8;
-int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes, int* cluster) {
+int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes, int* cluster, bool hinted = false) {
   int g = g_groups_override.load();
   if (g == 0) {
     const char* env = getenv("FF_TOPK_GROUPS");
@@ -161,15 +167,19 @@ int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes
   const size_t need = static_cast<size_t>(B) * ff::kWsRowWords * sizeof(uint32_t);
   if (workspace_bytes < need || g == 1) return 1;
   int c = *cluster;
-  if (g == 0) {
-    if (L_width < kGroupMinWidth || g_cluster_override.load() != 0) return 1;
+  const bool automatic = g == 0;
+  if (automatic) {
+    if (L_width < (hinted ? kGroupMinWidthHinted : kGroupMinWidth) || g_cluster_override.load() != 0) return 1;
     c = kGroupCluster;
-    g = static_cast<int>((L_width + c * 8192 - 1) / (static_cast<int64_t>(c) * 8192));   // one 32 KiB tile per CTA
+    g = 16;                                                     // more clusters than that bring nothing
+    const int64_t by_size = L_width / (static_cast<int64_t>(c) * 1024);   // at least 1 Ki columns per CTA
+    if (g > by_size) g = static_cast<int>(by_size);
   }
   int log2c = 0;
   while ((1 << log2c) < c) ++log2c;
   const int room = g_active_clusters[device][log2c] / (B > 0 ? B : 1);   // co-resident clusters per row
   if (g > room) g = room;
+  if (automatic && L_width < kGroupAlwaysWidth && g < 8) return 1;
   if (g > 64) g = 64;
   if (g < 2) return 1;
   *cluster = c;
@@ -274,7 +284,7 @@ int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k) {
 size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
   (void)k;
   // Only rows split over several clusters use scratch: long rows, small batches.
-  if (B < 1 || B > 16 || (L_width < kGroupMinWidth && g_groups_override.load() < 2)) return 0;
+  if (B < 1 || B > 16 || (L_width < kGroupMinWidthHinted && g_groups_override.load() < 2)) return 0;
   return static_cast<size_t>(B) * ff::kWsRowWords * sizeof(uint32_t);
 }
 
@@ -336,7 +346,7 @@ int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t
   p.hint_out = hint_out;
   int cluster = choose_cluster(device, B, L_width, k);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
-    p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster);
+    p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster, hint_in != nullptr);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
   return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
