@@ -39,7 +39,7 @@ FALLBACK_HBM_GBS = 6650.0
 ROTATE = 64
 # DRAM bytes per launch of the dominant kernel at the headline configuration,
 # from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 5000704   # split-row launch, profiles/topk_cluster_kernel_headline_B1_L1M_k2048.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 4357632   # split-row launch, profiles/topk_cluster_kernel_headline_B1_L1M_k2048.md
 
 
 # ---------------------------------------------------------------------------
