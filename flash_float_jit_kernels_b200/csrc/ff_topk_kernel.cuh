@@ -844,6 +844,10 @@ __device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C
   FF_TRACE(p, 30);
 }
 
+// How many scores the next call's guess should let through: between k (fewer is a miss) and
+// kSortCap (more is a miss), nearer to k because the finish costs grow with the square of it.
+__device__ __forceinline__ int hint_target_rank(int k) { return min(k + (k >> 2) + 64, kSortCap - (kSortCap >> 3)); }
+
 // Context-parallel send: the step of this launch and where its entries go in a peer's buffer.
 struct PushCtx {
   int64_t off;     // words from a peer's base to this rank's slot of this step's parity
@@ -1353,7 +1357,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     return;
   }
   const int T = min(expected_total, kSortCap);
-  const int hint_rank = min(T, k + (k >> 1)) - 1;
+  const int hint_rank = min(T, hint_target_rank(k)) - 1;
   if (my_share == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
     atomicOr(p.status, 1);
 
@@ -1409,7 +1413,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       if (valid && cnt == hint_rank) {
         const float va = __uint_as_float(bits_of_key(comp_key(c)));
         float guess = va;
-        const int want = k + (k >> 1);
+        const int want = hint_target_rank(k);
         if (T < want) {
           int best = 0;
           for (int g = 1; g < 32; ++g)
@@ -1598,7 +1602,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // from the ranks T/2 and T.  Two lanes of the row's first CTA each find one bucket by a
   // binary search over the buckets' suffix counts (the same in every CTA).
   if (kHinted && !HAS_MAP && p.hint_out != nullptr && my_share == 0 && tid < 32) {
-    const int want = k + (k >> 1);
+    const int want = hint_target_rank(k);
     const int rank_a = min(T, want) - 1;
     const int rank_m = T >> 1;
     const int rank_mine = (tid & 1) ? rank_m : rank_a;
