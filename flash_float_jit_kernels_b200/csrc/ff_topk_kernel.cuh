@@ -1400,8 +1400,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (valid && cnt < k)
       emit<kPush>(p, push, row, cnt, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
     if (kHinted && !HAS_MAP && p.hint_out != nullptr) {
-      // Next call's guess: the score of rank min(T, 3k/2) - 1, written by its owner.  With fewer
-      // than 3k/2 survivors that is the smallest one; its owner then extrapolates linearly below
+      // Next call's guess: the score of rank min(T, target) - 1 (hint_target_rank), written by its owner.  With fewer
+      // than `target` survivors that is the smallest one; its owner then extrapolates linearly below
       // it with the owned survivor whose rank is nearest to T/2 (ranks of the others are not known here).
       uint32_t* mid = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [32][3]: |rank - T/2|, value bits, rank
       if (tid < 32) {
@@ -1596,8 +1596,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
     if (pos < k) emit<kPush>(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
   }
-  // Next call's guess: a score of rank about 3k/2, so that about 3k/2 elements (between k and
-  // 4096) pass it on similar data.  With T >= 3k/2 survivors it is the lower edge of the bucket
+  // Next call's guess: a score of rank hint_target_rank(k), so that about that many elements (between k and
+  // 4096) pass it on similar data.  With at least that many survivors it is the lower edge of the bucket
   // that holds that rank; with fewer it is extrapolated linearly below the smallest survivor
   // from the ranks T/2 and T.  Two lanes of the row's first CTA each find one bucket by a
   // binary search over the buckets' suffix counts (the same in every CTA).

@@ -109,7 +109,7 @@ def fast_topk_v3(
             and skips the histogram exchange; a guess that does not fit costs one
             extra sweep (``FF_STATUS_HINT_MISSED`` in ``status``).  The result
             is the same exact top-k either way.  On return the entry holds a
-            score of rank about 1.5 k of this call's row: pass the tensor again
+            score of rank about 1.25 k of this call's row: pass the tensor again
             for the next call on similar rows (the next decode step).
 
     Returns:

@@ -116,7 +116,7 @@ int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t
  * of histograms, no second sweep.  If the guess does not fit, the row starts over
  * on the normal path and FF_STATUS_HINT_MISSED is OR-ed into `status`; the result
  * is exact and identical to ff_topk_launch's either way.  hint_out[i] (may be NULL,
- * may alias hint_in) receives a score of rank about 1.5 k of row i (NaN for rows with
+ * may alias hint_in) receives a score of rank about 1.25 k of row i (NaN for rows with
  * no more than k positions): a good guess for the next call on similar data, e.g. the
  * next decode step of the same sequences.  Device pointers, float32 [B]. */
 int ff_topk_launch_hinted(const float* scores, int64_t row_stride, const int32_t* lengths,
