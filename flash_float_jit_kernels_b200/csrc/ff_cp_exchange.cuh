@@ -87,30 +87,38 @@ struct RunSource {
 };
 
 // Waits for the value entries of all world x k candidates of the row and stages their
-// monotone keys in run_keys[world][k] (shared memory).  Four entries per thread are in
-// flight at a time.  Returns false (uniformly) if an entry did not arrive in time.
+// monotone keys in run_keys[world][k] (shared memory).  Sixteen entries per thread are in
+// flight at a time (with 8 ranks a thread of a 512-thread CTA stages 32 entries, and every
+// round of loads costs a trip to L2 or memory).  Returns false (uniformly) if an entry did
+// not arrive in time.
 __device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, int k, uint32_t step,
                                                uint32_t* run_keys) {
+  constexpr int kInFlight = 16;
   const int n_cand = world * k;
   const int nthreads = static_cast<int>(blockDim.x);
   const unsigned long long t0 = global_ns();
   bool ok = true;
-  for (int i0 = threadIdx.x; i0 < n_cand; i0 += 4 * nthreads) {
-    const uint32_t* ptr[4];
-    uint2 e[4];
+  for (int i0 = threadIdx.x; i0 < n_cand; i0 += kInFlight * nthreads) {
+    uint2 e[kInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * nthreads;
       if (i < n_cand) {
         const int q = i / k;
-        ptr[u] = src.value_entry(q, i - q * k);
-        e[u] = ld_entry(ptr[u]);
+        e[u] = ld_entry(src.value_entry(q, i - q * k));
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * nthreads;
-      if (i < n_cand) run_keys[i] = run_key_of_bits(await_entry(ptr[u], e[u], step, t0, ok));
+      if (i < n_cand) {
+        uint32_t bits = e[u].x;
+        if (e[u].y != step) {   // not there yet: poll (rare once the peers are in step)
+          const int q = i / k;
+          bits = await_entry(src.value_entry(q, i - q * k), e[u], step, t0, ok);
+        }
+        run_keys[i] = run_key_of_bits(bits);
+      }
     }
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
