@@ -556,7 +556,7 @@ def bench_cp(args):
                        "l2": f"each rank rotates over {n_rot} distinct 4 MiB shards (128 MiB > 126 MB L2)",
                        "timing": ("K steps in one CUDA graph replay" if graph is not None else
                                   "eager stream launches") + ", CUDA events, max over ranks",
-                       "exchange": ("self-validating 8-byte entries stored into every peer's receive buffer "
+                       "exchange": ("self-validating 16-byte entries stored into every peer's receive buffer "
                                     "over NVLink from the select kernel (32 KiB per rank per peer); the same "
                                     "launch polls its local entries and merges" if plan.exchange == "p2p" else
                                     "NCCL all-gather of (value, global index) candidates, 16 KiB per rank")},

@@ -13,7 +13,7 @@ Three steps per call, all on the current stream:
 
 Two exchanges are implemented.  ``p2p`` (default on GPUs): every rank stores its
 candidates straight into every peer's receive buffer over NVLink (peer memory
-mapped through CUDA IPC) as self-validating 8-byte entries ``{payload, step}``,
+mapped through CUDA IPC) as self-validating 16-byte entries ``{value, step, index, step}``,
 and the same kernel then polls its own (local) entries with a bounded wait and
 merges -- one kernel launch per step, no fence, no flag, no collective library
 call (``ff_topk_cp_step``).  ``nccl``: ``all_gather_into_tensor`` between

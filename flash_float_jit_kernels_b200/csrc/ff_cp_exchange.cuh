@@ -1,12 +1,13 @@
 // Context-parallel candidate exchange over peer memory (NVLink / NVSwitch).
 //
 // Every rank owns one allocation holding, for two alternating steps ("parities"),
-// a receive slot per rank.  A slot is two planes of 8-byte entries, one entry per
-// (row, position): {value bits, step} and {global index, step}.  The shard-local
-// select kernel stores each of its k candidates per row straight into EVERY
-// peer's slot as it ranks them, one 8-byte store per entry.  An 8-byte aligned
-// store arrives whole, so the step number inside the entry is its own "valid"
-// mark: the receiver polls an entry until it carries the current step (bounded
+// a receive slot per rank.  A slot holds one 16-byte entry per (row, position):
+// {value bits, step, global index, step}.  The shard-local select kernel stores
+// each of its k candidates per row straight into EVERY peer's slot as it ranks
+// them, one 16-byte store per candidate and peer (the link carries one packet
+// per store, so fewer and wider stores matter at 8 ranks).  An 8-byte aligned
+// half arrives whole, so the step number inside each half is its own "valid"
+// mark: the receiver polls a half until it carries the current step (bounded
 // wait).  No fence, no flag, no collective library call; the
 // receiver reads local memory only.
 // The reference has no multi-GPU path; semantics follow fast_topk_v3
@@ -43,8 +44,9 @@ __device__ __forceinline__ uint32_t run_key_of_bits(uint32_t bits) {
   return bits == kNoCandidateBits ? 0u : key_of_bits(bits);
 }
 
-__device__ __forceinline__ void st_entry(uint32_t* entry, uint32_t payload, uint32_t step) {
-  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(entry), "r"(payload), "r"(step) : "memory");
+__device__ __forceinline__ void st_entry(uint32_t* entry, uint32_t value_bits, uint32_t gidx, uint32_t step) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(entry), "r"(value_bits), "r"(step), "r"(gidx)
+               : "memory");
 }
 __device__ __forceinline__ uint2 ld_entry(const uint32_t* entry) {
   uint2 e;
@@ -75,14 +77,13 @@ __device__ __forceinline__ uint32_t await_entry(const uint32_t* entry, uint2 fir
 // Where the receive slots of one step and one row are.
 struct RunSource {
   const uint32_t* base;   // this rank's receive area of the step's parity: [world][slot_words]
-  int64_t slot_words;     // per rank: value plane then index plane, 2 words per (row, position)
-  int64_t plane_words;    // 2 * B * k
-  int64_t row_words;      // 2 * row * k
-  __device__ __forceinline__ const uint32_t* value_entry(int q, int j) const {
-    return base + q * slot_words + row_words + 2 * j;
+  int64_t slot_words;     // per rank: 4 words per (row, position)
+  int64_t row_words;      // 4 * row * k
+  __device__ __forceinline__ const uint32_t* value_entry(int q, int j) const {   // the {value bits, step} half
+    return base + q * slot_words + row_words + 4 * j;
   }
-  __device__ __forceinline__ const uint32_t* index_entry(int q, int j) const {
-    return base + q * slot_words + plane_words + row_words + 2 * j;
+  __device__ __forceinline__ const uint32_t* index_entry(int q, int j) const {   // the {global index, step} half
+    return base + q * slot_words + row_words + 4 * j + 2;
   }
 };
 
@@ -197,8 +198,7 @@ __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergePara
   RunSource src;
   src.base = p.recv_even + static_cast<int64_t>(step & 1u) * p.parity_words;
   src.slot_words = p.slot_words;
-  src.plane_words = 2 * static_cast<int64_t>(p.B) * k;
-  src.row_words = 2 * static_cast<int64_t>(row) * k;
+  src.row_words = 4 * static_cast<int64_t>(row) * k;
   bool ok = stage_run_keys(src, p.world, k, step, run_keys);
   const int begin = blockIdx.x * blockDim.x;
   const int end = min(p.world * k, begin + static_cast<int>(blockDim.x));

@@ -500,7 +500,7 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
 
 struct FfCpExchange {
   int world, rank, B, k, device;
-  size_t slot_words;     // one rank's candidate block: value plane then index plane, 8-byte entries (4*B*k words)
+  size_t slot_words;     // one rank's candidate block: a 16-byte entry per (row, position) (4*B*k words)
   size_t ctrl_offset;    // words from the allocation's start to the control words
   size_t send_offset;    // words from the allocation's start to the send block
   size_t total_bytes;

@@ -862,16 +862,11 @@ template <bool PUSH>
 __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, int row, int j, int32_t idx,
                                      uint32_t key, bool is_map, int table_row) {
   if (PUSH) {
-    // one self-validating 8-byte entry per plane and peer: {payload, step}
+    // one self-validating 16-byte entry per peer: {value bits, step, global index, step}
     const uint32_t vbits = idx < 0 ? kNoCandidateBits : bits_of_key(key);
     const uint32_t gidx = idx < 0 ? 0xffffffffu : static_cast<uint32_t>(idx + p.shard_offset);
-    const size_t at = 2 * (static_cast<size_t>(row) * p.k + j);
-    const size_t plane = 2 * static_cast<size_t>(p.B) * p.k;
-    for (int q = 0; q < p.push_world; ++q) {
-      uint32_t* slot = p.push_peers.base[q] + push.off;
-      st_entry(slot + at, vbits, push.step);
-      st_entry(slot + plane + at, gidx, push.step);
-    }
+    const size_t at = push.off + 4 * (static_cast<size_t>(row) * p.k + j);
+    for (int q = 0; q < p.push_world; ++q) st_entry(p.push_peers.base[q] + at, vbits, gidx, push.step);
     return;
   }
   int32_t o;
@@ -1683,8 +1678,7 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
         RunSource src;
         src.base = p.push_peers.base[p.push_rank] + static_cast<int64_t>(push.step & 1u) * world * p.push_slot_words;
         src.slot_words = p.push_slot_words;
-        src.plane_words = 2 * static_cast<int64_t>(p.B) * k;
-        src.row_words = 2 * static_cast<int64_t>(row) * k;
+        src.row_words = 4 * static_cast<int64_t>(row) * k;
         uint32_t* run_keys = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [world][k], at most 128 KiB
         __syncthreads();   // the ring region is free in the whole CTA
         bool ok = stage_run_keys(src, world, k, push.step, run_keys);

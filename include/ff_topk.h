@@ -167,7 +167,7 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
 /* ---- Context-parallel mode with the exchange fused over peer memory --------
  * (No reference counterpart.)  Instead of a collective library call, each rank
  * stores its candidates straight into every peer's receive buffer over NVLink as
- * self-validating 8-byte entries {payload, step}; the merge polls its own (local)
+ * self-validating 16-byte entries {value bits, step, global index, step}; the merge polls its own (local)
  * entries until they carry the current step (bounded to one second,
  * FF_STATUS_WAIT_TIMEOUT on expiry).  No fence, flag or collective call.
  *
