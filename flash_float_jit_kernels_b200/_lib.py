@@ -64,6 +64,16 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_size_t, c_void_p,
          c_void_p],
     ),
+    "ff_topk_cp_send_hinted": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_size_t,
+         c_void_p, c_void_p],
+    ),
+    "ff_topk_cp_step_hinted": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+         c_size_t, c_void_p, c_void_p],
+    ),
     "ff_topk_cp_merge": (
         c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int32, c_int32,

@@ -115,16 +115,18 @@ class ContextParallelTopk:
             _lib.load().ff_cp_exchange_destroy(self._ex)
             self._ex = None
 
-    def _step_p2p(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> None:
+    def _step_p2p(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int,
+                  threshold_hint: Optional[torch.Tensor] = None) -> None:
         lib = _lib.load()
         B, L = score_shard.size(0), score_shard.size(1)
         ws, ws_bytes = _workspace(lib, score_shard.device, B, L, self.k)
+        hint = threshold_hint.data_ptr() if threshold_hint is not None else None
         with torch.cuda.device(score_shard.device):
-            rc = lib.ff_topk_cp_step(
+            rc = lib.ff_topk_cp_step_hinted(
                 self._ex, score_shard.data_ptr(), score_shard.stride(0) if B > 1 else max(score_shard.stride(0), L),
-                lengths.data_ptr(), self.out.data_ptr(), L, shard_offset, _ptr(ws), ws_bytes, None,
+                lengths.data_ptr(), self.out.data_ptr(), L, shard_offset, hint, hint, _ptr(ws), ws_bytes, None,
                 _stream_ptr(score_shard.device))
-        _lib.check(rc, "ff_topk_cp_step")
+        _lib.check(rc, "ff_topk_cp_step_hinted")
 
     # -- step 1 ---------------------------------------------------------
     def _local(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> None:
@@ -157,16 +159,26 @@ class ContextParallelTopk:
                 _ptr(ws), ws_bytes, None, _stream_ptr(self.device))
         _lib.check(rc, "ff_topk_cp_merge")
 
-    def __call__(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int) -> torch.Tensor:
+    def __call__(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int,
+                 threshold_hint: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``score_shard``: (B, L_local) columns ``[shard_offset, shard_offset+L_local)``
         of the full rows; ``lengths``: (B) int32 GLOBAL row lengths (identical on
-        every rank).  Returns (B, k) int32 global indices, identical on every rank."""
+        every rank).  Returns (B, k) int32 global indices, identical on every rank.
+
+        ``threshold_hint``: optional (B) float32 tensor of THIS rank
+        (:func:`new_threshold_hint`), read and updated: guesses for the shard-local
+        select, with the meaning of ``fast_topk_v3(threshold_hint=...)``.  Used by the
+        peer-memory exchange only; the result is exact with or without it."""
+        if threshold_hint is not None:
+            _require(threshold_hint.shape == (self.B,) and threshold_hint.dtype == torch.float32
+                     and threshold_hint.is_contiguous() and threshold_hint.device == score_shard.device,
+                     "threshold_hint must be a contiguous (B) float32 tensor on score_shard's device")
         _require(score_shard.dim() == 2 and score_shard.size(0) == self.B, "score_shard must be [B, L_local]")
         _require(lengths.dim() == 1 and lengths.size(0) == self.B and lengths.dtype == torch.int32
                  and lengths.is_contiguous(), "lengths must be contiguous int32 [B]")
         _require(shard_offset >= 0, "shard_offset must be >= 0")
         if self._ex is not None:
-            self._step_p2p(score_shard, lengths, int(shard_offset))
+            self._step_p2p(score_shard, lengths, int(shard_offset), threshold_hint)
             return self.out
         self._local(score_shard, lengths, int(shard_offset))
         self._exchange()

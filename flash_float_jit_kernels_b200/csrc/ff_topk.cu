@@ -93,6 +93,7 @@ void init_device(int device) {
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePlain>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePush>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePushHinted>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true, ff::kModePlain>);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(ff::cp_merge_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -208,9 +209,12 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
 
   // one instantiation per mode: the plain select carries no code of the others
   cudaError_t e;
-  if (!HAS_MAP && q.push_world > 0)
+  const bool hints = q.hint_in != nullptr || q.hint_out != nullptr;
+  if (!HAS_MAP && q.push_world > 0 && hints)
+    e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePushHinted>, q);
+  else if (!HAS_MAP && q.push_world > 0)
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePush>, q);
-  else if (!HAS_MAP && (q.hint_in != nullptr || q.hint_out != nullptr))
+  else if (!HAS_MAP && hints)
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted>, q);
   else
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<HAS_MAP, ff::kModePlain>, q);
@@ -611,8 +615,9 @@ int cp_fused_setting() {
 // fused_out == nullptr: send only (the merge is a later launch).  Otherwise the launch
 // merges too, if all its CTAs fit on the device together; *did_fuse tells.
 int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
-                 int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
-                 int32_t* status, void* stream, int32_t* fused_out, bool* did_fuse) {
+                 int64_t L_width, int64_t shard_offset, const float* hint_in, float* hint_out,
+                 void* workspace, size_t workspace_bytes, int32_t* status, void* stream, int32_t* fused_out,
+                 bool* did_fuse) {
   if (did_fuse != nullptr) *did_fuse = false;
   if (handle == nullptr) return fail(FF_ERR_NULL, "exchange handle must not be NULL");
   FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
@@ -646,9 +651,11 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
   p.push_rank = ex->rank;
   p.push_slot_words = static_cast<int64_t>(ex->slot_words);
   p.push_ctrl_offset = static_cast<int64_t>(ex->ctrl_offset);
+  p.hint_in = hint_in;     // guesses of the shard-local threshold, as in ff_topk_launch_hinted
+  p.hint_out = hint_out;
   int cluster = choose_cluster(device, ex->B, L_width, ex->k);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
-    p.groups = choose_groups(device, ex->B, L_width, workspace_bytes, &cluster);
+    p.groups = choose_groups(device, ex->B, L_width, workspace_bytes, &cluster, hint_in != nullptr);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
   if (fused_out != nullptr && cp_fused_setting() != 0) {
@@ -671,8 +678,15 @@ extern "C" {
 int ff_topk_cp_send(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
                     int64_t L_width, int64_t shard_offset, void* workspace, size_t workspace_bytes,
                     int32_t* status, void* stream) {
-  return cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, workspace, workspace_bytes,
-                      status, stream, nullptr, nullptr);
+  return cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, nullptr, nullptr, workspace,
+                      workspace_bytes, status, stream, nullptr, nullptr);
+}
+
+int ff_topk_cp_send_hinted(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                           int64_t L_width, int64_t shard_offset, const float* hint_in, float* hint_out,
+                           void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  return cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, hint_in, hint_out, workspace,
+                      workspace_bytes, status, stream, nullptr, nullptr);
 }
 
 int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx, int32_t* status,
@@ -703,10 +717,18 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
 int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
                     int32_t* out_idx, int64_t L_width, int64_t shard_offset, void* workspace,
                     size_t workspace_bytes, int32_t* status, void* stream) {
+  return ff_topk_cp_step_hinted(handle, scores, row_stride, lengths, out_idx, L_width, shard_offset, nullptr,
+                                nullptr, workspace, workspace_bytes, status, stream);
+}
+
+int ff_topk_cp_step_hinted(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                           int32_t* out_idx, int64_t L_width, int64_t shard_offset, const float* hint_in,
+                           float* hint_out, void* workspace, size_t workspace_bytes, int32_t* status,
+                           void* stream) {
   if (out_idx == nullptr) return fail(FF_ERR_NULL, "out_idx must not be NULL");
   bool fused = false;
-  const int rc = cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, workspace,
-                              workspace_bytes, status, stream, out_idx, &fused);
+  const int rc = cp_send_impl(handle, scores, row_stride, lengths, L_width, shard_offset, hint_in, hint_out,
+                              workspace, workspace_bytes, status, stream, out_idx, &fused);
   if (rc != 0 || fused) return rc;
   return ff_topk_cp_recv_merge(handle, lengths, out_idx, status, stream);
 }

@@ -895,16 +895,17 @@ __device__ __forceinline__ float prefilter_value(uint32_t key_lo) {
 
 // MODE selects what is compiled in besides the plain select, so that the plain kernel
 // carries no code of the others: kModeHinted = threshold guesses (hint_in / hint_out),
-// kModePush = context-parallel send (and single-kernel step).
+// kModePush = context-parallel send (and single-kernel step); the two are bits and combine.
 constexpr int kModePlain = 0;
 constexpr int kModeHinted = 1;
 constexpr int kModePush = 2;
+constexpr int kModePushHinted = kModePush | kModeHinted;
 
 template <bool HAS_MAP, int MODE>
 __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
                                               const PushCtx& push) {
-  constexpr bool kPush = MODE == kModePush;
-  constexpr bool kHinted = MODE == kModeHinted;
+  constexpr bool kPush = (MODE & kModePush) != 0;
+  constexpr bool kHinted = (MODE & kModeHinted) != 0;
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
   uint32_t* merged = reinterpret_cast<uint32_t*>(smem + kSmemStage);
@@ -1626,7 +1627,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 
 template <bool HAS_MAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
-  constexpr bool kPush = MODE == kModePush;
+  constexpr bool kPush = (MODE & kModePush) != 0;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ ClusterShared sh;
   // Context-parallel send: this launch also delivers its result to the peers.  The step number is

@@ -179,6 +179,11 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
  *   ff_topk_cp_recv_merge      wait for all peers' entries of the current step + merge (1 launch)
  *   ff_topk_cp_step            the whole step as ONE launch (select, store to peers, poll, merge) when
  *                              all CTAs of the launch can be resident at once; else send + recv_merge
+ *   ff_topk_cp_send_hinted / ff_topk_cp_step_hinted
+ *                              the same with threshold guesses for the shard-local select: hint_in /
+ *                              hint_out are [B] floats of THIS rank's shard, with the meaning and the
+ *                              miss behaviour (FF_STATUS_HINT_MISSED, result still exact) of
+ *                              ff_topk_launch_hinted; either may be NULL
  * Every rank must call the step functions the same number of times in the same
  * order; a rank may run at most one step ahead of its peers (two alternating
  * receive buffers).  out_idx is [B, k] global indices, identical on all ranks. */
@@ -197,6 +202,13 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
 int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
                     int32_t* out_idx, int64_t L_width, int64_t shard_offset, void* workspace,
                     size_t workspace_bytes, int32_t* status, void* stream);
+int ff_topk_cp_send_hinted(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                           int64_t L_width, int64_t shard_offset, const float* hint_in, float* hint_out,
+                           void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+int ff_topk_cp_step_hinted(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
+                           int32_t* out_idx, int64_t L_width, int64_t shard_offset, const float* hint_in,
+                           float* hint_out, void* workspace, size_t workspace_bytes, int32_t* status,
+                           void* stream);
 
 /* Test / tuning hook: force the thread-block-cluster size per row
  * (0 = automatic policy, else 1, 2, 4, 8 or 16).  Process-wide. */

@@ -257,3 +257,96 @@ def test_single_kernel_step_with_a_missing_peer_times_out():
         torch.cuda.synchronize()
         for h in exs:
             lib.ff_cp_exchange_destroy(h)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("P,L", [(2, 600000), (4, 2400000)])
+def test_peer_exchange_with_threshold_guesses(oracle, P, L):
+    """Every rank keeps guesses for its own shard (read and updated in place).  Consecutive steps
+    score slowly drifting rows, so the guesses of the second step on hit; a wild jump makes them
+    miss, which is reported and costs a histogram pass but never exactness."""
+    from flash_float_jit_kernels_b200 import _lib, new_threshold_hint, shard_bounds
+    from flash_float_jit_kernels_b200.topk_indexer import _ptr, _workspace
+    lib = _lib.load()
+    lib.ff_topk_set_cluster_override(0)
+    dev = torch.device("cuda:0")
+    B, k = 2, 1024
+    exs = _make_exchanges(lib, P, B, k)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        hints = [new_threshold_hint(B, dev) for _ in range(P)]
+        base = torch.randn((B, L), generator=torch.Generator().manual_seed(41)).to(torch.bfloat16).float()
+        shard_len = shard_bounds(L, P, 0)[1]
+        ws, ws_bytes = _workspace(lib, dev, B, shard_len + 8, k)
+        seen = []
+        for step in range(5):
+            drift = 0.01 * torch.randn((B, L), generator=torch.Generator().manual_seed(50 + step))
+            s = (base + drift).to(torch.bfloat16).float()
+            if step == 3:
+                s = s * 4.0 + 10.0           # the old guesses are far too low now: too many survivors
+            lengths = torch.tensor([L, L - 12345], dtype=torch.int32)
+            sd, ld = s.to(dev), lengths.to(dev)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            for r in range(P):
+                a, b = shard_bounds(L, P, r)
+                shard = sd[:, a:b]
+                assert lib.ff_topk_cp_send_hinted(exs[r], shard.data_ptr(), shard.stride(0), ld.data_ptr(), b - a, a,
+                                                  hints[r].data_ptr(), hints[r].data_ptr(), _ptr(ws), ws_bytes,
+                                                  status.data_ptr(), stream) == 0
+            outs = torch.empty((P, B, k), dtype=torch.int32, device=dev)
+            for r in range(P):
+                assert lib.ff_topk_cp_recv_merge(exs[r], ld.data_ptr(), outs[r].data_ptr(), status.data_ptr(),
+                                                 stream) == 0
+            torch.cuda.synchronize()
+            seen.append(int(status.item()))
+            assert seen[-1] & ~_lib.FF_STATUS_HINT_MISSED == 0
+            exp = oracle.topk_c(s.numpy(), lengths.numpy(), k)
+            for r in range(P):
+                assert np.array_equal(outs[r].cpu().numpy(), exp), f"step {step} rank {r}"
+            for r in range(P):
+                assert not torch.isnan(hints[r]).any(), "every shard is longer than k: a guess comes back"
+        assert seen[0] == 0, "NaN guesses are no guesses, so nothing can miss"
+        assert seen[1] == 0 and seen[2] == 0, "guesses from the previous step should hit on drifting rows"
+        assert seen[3] == _lib.FF_STATUS_HINT_MISSED
+    finally:
+        torch.cuda.synchronize()
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
+
+
+@pytest.mark.gpu
+def test_single_kernel_step_with_threshold_guesses(oracle):
+    """world == 1, one launch per step, guesses carried from step to step; the row is split over
+    clusters (1 Mi) or not (70000)."""
+    import ctypes
+    from flash_float_jit_kernels_b200 import _lib, new_threshold_hint
+    from flash_float_jit_kernels_b200.topk_indexer import _ptr, _workspace
+    lib = _lib.load()
+    lib.ff_topk_set_cluster_override(0)
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream().cuda_stream
+    for (B, L, k) in ((1, 1 << 20, 2048), (3, 70000, 512)):
+        h = ctypes.c_void_p()
+        assert lib.ff_cp_exchange_create(1, 0, B, k, ctypes.byref(h)) == 0
+        try:
+            ws, ws_bytes = _workspace(lib, dev, B, L, k)
+            hint = new_threshold_hint(B, dev)
+            out = torch.empty((B, k), dtype=torch.int32, device=dev)
+            base = torch.randn((B, L), generator=torch.Generator().manual_seed(900)).to(torch.bfloat16).float()
+            for step in range(4):
+                drift = 0.01 * torch.randn((B, L), generator=torch.Generator().manual_seed(901 + step))
+                s = (base + drift).to(torch.bfloat16).float()
+                lengths = torch.full((B,), L - 17 * step, dtype=torch.int32)
+                sd, ld = s.to(dev), lengths.to(dev)
+                status = torch.zeros(1, dtype=torch.int32, device=dev)
+                launches = lib.ff_topk_launch_count()
+                assert lib.ff_topk_cp_step_hinted(h, sd.data_ptr(), sd.stride(0), ld.data_ptr(), out.data_ptr(), L, 0,
+                                                  hint.data_ptr(), hint.data_ptr(), _ptr(ws), ws_bytes,
+                                                  status.data_ptr(), stream) == 0
+                assert lib.ff_topk_launch_count() - launches == 1, "the step should be a single launch"
+                torch.cuda.synchronize()
+                assert int(status.item()) == 0, (B, step)
+                assert np.array_equal(out.cpu().numpy(), oracle.topk_c(s.numpy(), lengths.numpy(), k)), (B, step)
+        finally:
+            torch.cuda.synchronize()
+            lib.ff_cp_exchange_destroy(h)
