@@ -454,8 +454,13 @@ def bench_cp(args):
     plan = ContextParallelTopk(1, k, dev, exchange=args.exchange)
     offset = rank * L_SHARD
 
+    hint = None
+    if args.threshold_hint:                                          # secondary measurement, not the default line
+        from flash_float_jit_kernels_b200 import new_threshold_hint
+        hint = new_threshold_hint(1, dev)
+
     def step(i):
-        return plan(shards[i % n_rot].unsqueeze(0), lengths, offset)
+        return plan(shards[i % n_rot].unsqueeze(0), lengths, offset, threshold_hint=hint)
 
     for i in range(W):
         step(i)
@@ -553,6 +558,7 @@ def bench_cp(args):
             "config": {"workload": f"context-parallel B=1 L={L} k=2048 bf16-rounded N(0,1), "
                                    f"{world} contiguous shards of {L_SHARD} columns",
                        "B": 1, "L": L, "k": k, "parallelism": f"cp{world}",
+                       "threshold_hint": bool(args.threshold_hint),
                        "l2": f"each rank rotates over {n_rot} distinct 4 MiB shards (128 MiB > 126 MB L2)",
                        "timing": ("K steps in one CUDA graph replay" if graph is not None else
                                   "eager stream launches") + ", CUDA events, max over ranks",
@@ -634,6 +640,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary configurations")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch the steps eagerly instead of replaying a graph")
+    ap.add_argument("--threshold-hint", action="store_true",
+                    help="N > 1: every rank carries a threshold guess for its shard from step to step")
     ap.add_argument("--exchange", default="auto", choices=["auto", "p2p", "nccl"], help="N > 1: candidate exchange")
     ap.add_argument("--profile-case", default=None, choices=["headline", "unique16k", "b64", "logits"],
                     help="run a few eager launches of one configuration and exit (for ncu)")
