@@ -9,9 +9,18 @@ in HBM and rotate over 64 distinct 4 MiB rows (256 MiB > the 126 MB L2) so
 every step reads cold data.  The K timed steps are replayed from one CUDA graph
 and bracketed by CUDA events.
 N > 1 (under torchrun): context-parallel mode, weak scaling: every rank holds a
-1,048,576-column shard of one row of length N x 1,048,576; one step is local
-select + NCCL all-gather of the candidates + merge.  Time is the max over
-ranks.
+1,048,576-column shard of one row of length N x 1,048,576; one step is ONE
+kernel launch per rank (shard-local select, candidates stored into the peers
+over NVLink, merge).  Time is the max over ranks.  Before anything is timed the
+context-parallel result is compared, on every rank, with the one-GPU operator
+on the gathered row (``parity_checked``); ``extra.c5`` adds the long-context
+configuration (fp32 N(0,1), L = 4 Mi and 8 Mi split over the N ranks) beside
+rank 0's one-GPU time on the same rows.
+
+The graph of K steps is replayed until at least 50 ms of device time have
+passed; ``value`` is the median per-step time over the replays and
+``quantiles`` holds p20 / p50 / p80 (the reference benchmark reports the same
+three, ``benchmark/bench_topk.py:374-381``).
 
 Prints ONE JSON line (rank 0).  ``--impl reference`` times ``torch.topk`` on
 the host cores for the same configuration (the CPU statement of the path).
@@ -19,6 +28,7 @@ the host cores for the same configuration (the CPU statement of the path).
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -37,9 +47,10 @@ PUBLISHED_US = 110.7          # fast_topk_v3, B=1, L=1,048,576, k=2048 (GB300/B3
 NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 ROTATE = 64
-# DRAM bytes per launch of the dominant kernel at the headline configuration,
-# from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 4357632   # split-row launch, profiles/topk_cluster_kernel_headline_B1_L1M_k2048.md
+# The reference has no CPU implementation of this path (its kernels are CUDA only); the CPU arm
+# times the comparator the path is specified against.
+CPU_IMPL_NOTE = "torch.topk on the host cores: the CPU statement of the path (the reference's own code is CUDA only)"
+MIN_TIMED_MS = 50.0           # replays are repeated until this much device time has been measured
 
 
 # ---------------------------------------------------------------------------
@@ -121,6 +132,52 @@ class ClockSampler:
                 "samples": len(win), "scope": scope}
 
 
+def measured_traffic(case: str):
+    """DRAM bytes per launch of the dominant kernel from the last ncu capture of `case`, with the
+    commit it was captured at (flash_float_jit_kernels_b200/measured_traffic.json), or None."""
+    p = ROOT / "flash_float_jit_kernels_b200" / "measured_traffic.json"
+    try:
+        rec = json.loads(p.read_text())[case]
+        return int(rec["dram_bytes_per_launch"]), str(rec.get("commit", "unknown"))
+    except Exception:
+        return None, None
+
+
+def launch_shape(lib, B, L, k, hinted=False):
+    """(CTAs per cluster, clusters per row) of the launch the operator makes for this shape."""
+    out = (ctypes.c_int32 * 2)()
+    lib.ff_topk_policy_launch_shape(B, L, k, 1, 1 if hinted else 0, out)
+    return int(out[0]), int(out[1])
+
+
+def quantiles(samples):
+    """p20 / p50 / p80 of a list (nearest rank), as the reference benchmark reports them."""
+    v = sorted(samples)
+    pick = lambda q: v[min(len(v) - 1, int(q * len(v)))]
+    return {"p20": round(pick(0.2), 3), "p50": round(pick(0.5), 3), "p80": round(pick(0.8), 3), "n": len(v)}
+
+
+def timed_replays(graph, stream, steps_per_replay: int, min_ms: float = MIN_TIMED_MS, max_replays: int = 4000):
+    """Replays `graph` back to back on `stream` until min_ms of device time have been measured
+    (at least 10 replays); returns the per-step time in us of every replay (CUDA events between
+    the replays, on the replay stream)."""
+    per_step_us = []
+    total_ms = 0.0
+    while (total_ms < min_ms or len(per_step_us) < 10) and len(per_step_us) < max_replays:
+        n = 10
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        ev[0].record(stream)
+        for i in range(n):
+            graph.replay()
+            ev[i + 1].record(stream)
+        stream.synchronize()
+        for i in range(n):
+            ms = ev[i].elapsed_time(ev[i + 1])
+            total_ms += ms
+            per_step_us.append(ms * 1e3 / steps_per_replay)
+    return per_step_us
+
+
 def make_rows(n_rows: int, L: int, device, seed: int) -> torch.Tensor:
     """bf16-rounded N(0,1) rows (heavy ties), one distinct row per rotation slot."""
     g = torch.Generator(device=device)
@@ -172,29 +229,20 @@ def bench_single(args):
         side.synchronize()
         sampler = ClockSampler(0)
         sampler.start()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        e0.record(side)
-        graph.replay()
-        e1.record(side)
-        side.synchronize()
+        samples = timed_replays(graph, side, K)
         t1 = time.perf_counter()
-        total_ms = e0.elapsed_time(e1)
-        # keep the sampler running over a few more replays so short runs still get samples
         clocks = sampler.summary(t0, t1)
-        if clocks.get("scope") != "timed_region":
-            t0b = time.perf_counter()
-            while time.perf_counter() - t0b < 0.05:
-                graph.replay()
-            side.synchronize()
-            clocks = sampler.summary(t0b, time.perf_counter())
-            clocks["scope"] = "identical_replays_after_timed_region"
         sampler.stop()
-    us = total_ms * 1e3 / K
+    q = quantiles(samples)
+    us = q["p50"]
+    q["mean"] = round(sum(samples) / len(samples), 3)
     peak, peak_src = measured_peak()
     algo_bytes = 4 * L
     achieved = algo_bytes / (us * 1e-6) / 1e9
+    traffic, traffic_commit = measured_traffic("headline_B1_L1M_k2048")
+    shape = launch_shape(lib, 1, L, k)
 
     # ---- end to end through the public operator with host buffers ----------
     host_in = torch.empty((1, L), dtype=torch.float32).pin_memory()
@@ -202,24 +250,27 @@ def bench_single(args):
     host_out = torch.empty((1, k), dtype=torch.int32).pin_memory()
     dev_in = torch.empty((1, L), dtype=torch.float32, device=dev)
     dev_out = torch.empty((1, k), dtype=torch.int32, device=dev)
-    Ke = min(K, 500)
+    Ke = max(200, min(K, 1000))
 
     def e2e_step():
         dev_in.copy_(host_in, non_blocking=True)
         fast_topk_v3(dev_in, lengths, k, out=dev_out)
         host_out.copy_(dev_out, non_blocking=True)
 
-    for _ in range(3):
+    for _ in range(5):
         e2e_step()
     torch.cuda.synchronize()
-    e2e_mode = "eager calls on the current stream"   # (one CUDA graph replay per step measured slower: 262 us)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(Ke):
+    e2e_mode = "eager calls on the current stream, one CUDA event pair per step"
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(Ke + 1)]
+    ev[0].record()
+    for i in range(Ke):
         e2e_step()
-    e1.record()
+        ev[i + 1].record()
     torch.cuda.synchronize()
-    e2e_us = e0.elapsed_time(e1) * 1e3 / Ke
+    e2e_samples = [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(Ke)]
+    e2e_q = quantiles(e2e_samples)
+    e2e_us = e2e_q["p50"]
+    e2e_q["mean"] = round(sum(e2e_samples) / Ke, 3)
 
     extra = {}
     if not args.no_extra:
@@ -230,17 +281,21 @@ def bench_single(args):
         "metric": "topk_us_per_call", "value": round(us, 3), "unit": "us", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(us / 1e3, 6), "higher_is_better": False, "scaling": "weak",
         "vs_baseline": round(us / PUBLISHED_US, 4), "dtype": "f32->u32 keys", "data": "synthetic",
+        "quantiles": q,
         "config": {"workload": "B=1 L=1048576 k=2048 bf16-rounded N(0,1) (heavy ties)", "B": 1, "L": L, "k": k,
                    "l2": f"inputs rotate over {ROTATE} distinct 4 MiB rows (256 MiB > 126 MB L2)",
-                   "timing": "K steps in one CUDA graph replay, CUDA events on the replay stream",
-                   "cluster_size": int(lib.ff_topk_policy_cluster_size(1, L, k))},
+                   "timing": f"K steps in one CUDA graph, replayed {len(samples)} times (>= {MIN_TIMED_MS:.0f} ms), CUDA "
+                             "events between the replays on the replay stream; value = median per-step time",
+                   "launch_shape": {"cluster_size": int(shape[0]), "clusters_per_row": int(shape[1]),
+                                    "ctas": int(shape[0]) * int(shape[1])},
+                   "vs_baseline_note": "published figure is for GB300/B300 (reference README.md:52): cross-hardware"},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 5), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                     "frac": round(achieved / peak, 5), "traffic": traffic, "traffic_captured_at_commit": traffic_commit,
                      "peak_source": peak_src, "algorithmic_bytes_per_launch": algo_bytes,
                      "frac_of_nominal_8TBs": round(achieved / NOMINAL_HBM_GBS, 5)},
         "cpu_baseline": cpu,
         "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": 4 * L, "d2h_bytes_per_step": 4 * k,
-                "steps": Ke, "mode": e2e_mode},
+                "steps": Ke, "mode": e2e_mode, "quantiles": e2e_q},
         "gpu_launches": int(launches_per_replay),
         "clocks": clocks,
         "extra": extra,
@@ -290,7 +345,8 @@ def bench_extras(dev, lib, peak):
                                "algorithmic_read_bytes": int(4 * valid), "achieved_gbs": round(gbs, 1),
                                "frac_of_measured_peak": round(gbs / peak, 4),
                                "frac_of_nominal_8TBs": round(gbs / NOMINAL_HBM_GBS, 4),
-                               "cluster_size": int(lib.ff_topk_policy_cluster_size(64, 131072, K_TOP))}
+                               "launch_shape": dict(zip(("cluster_size", "clusters_per_row"),
+                                                        launch_shape(lib, 64, 131072, K_TOP)))}
     del batches
     sweep = {}
     for L in (16384, 65536, 131072, 262144, 524288):
@@ -393,7 +449,8 @@ def cpu_baseline(score_cpu: torch.Tensor, k: int, seconds: float):
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
         n += 1
-    return {"value": round(best * 1e6, 1), "unit": "us", "cores": cores, "kind": "reference",
+    return {"value": round(best * 1e6, 1), "unit": "us", "cores": cores, "kind": "port",
+            "implementation": CPU_IMPL_NOTE,
             "sample": f"torch.topk on the host cores, same row (B={score_cpu.shape[0]}, L={score_cpu.shape[1]}, "
                       f"k={k}), best of {n} calls in {seconds:.0f} s"}
 
@@ -426,7 +483,8 @@ def bench_reference(args):
         "scaling": "weak", "vs_baseline": round(us / PUBLISHED_US, 3), "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"B=1 L={L} k=2048 bf16-rounded N(0,1) (heavy ties), torch.topk on host cores",
                    "B": 1, "L": L, "k": K_TOP},
-        "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "reference",
+        "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
+                         "implementation": CPU_IMPL_NOTE,
                          "sample": f"{done} full-row torch.topk calls (time budget {budget_s:.0f} s)"},
         "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -436,9 +494,119 @@ def bench_reference(args):
 # ---------------------------------------------------------------------------
 # ours, N > 1: context-parallel weak scaling
 # ---------------------------------------------------------------------------
+def _cp_graph(plan, step, K, lib, side, args, dist, dev):
+    """Captures K steps into one CUDA graph when the peer-memory exchange is in use (a step is
+    one kernel launch and no library call; the step counter lives in device memory).  All ranks
+    replay a graph, or none does."""
+    graph, launches = None, 0
+    if plan.exchange == "p2p" and not args.no_graph:
+        try:
+            with torch.cuda.stream(side):
+                before = lib.ff_topk_launch_count()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for i in range(K):
+                        step(i)
+                launches = lib.ff_topk_launch_count() - before
+            graph = g
+        except Exception:
+            graph = None
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        graph = None
+    return graph, launches
+
+
+def _cp_time(plan, step, K, lib, args, dist, dev, min_ms=MIN_TIMED_MS):
+    """Per-step times (us, max over ranks per replay) of the context-parallel step."""
+    side = torch.cuda.Stream()
+    graph, launches = _cp_graph(plan, step, K, lib, side, args, dist, dev)
+    if graph is not None:
+        with torch.cuda.stream(side):
+            graph.replay()                                  # untimed: upload + warm-up
+        side.synchronize()
+    # every rank must make the same number of replays: agree on it from a first timed one
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def one_replay():
+        if graph is not None:
+            with torch.cuda.stream(side):
+                e0.record(side)
+                graph.replay()
+                e1.record(side)
+            side.synchronize()
+        else:
+            e0.record()
+            for i in range(K):
+                step(i)
+            e1.record()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+
+    first = torch.tensor([one_replay()], device=dev)
+    dist.all_reduce(first, op=dist.ReduceOp.MAX)
+    n_rep = int(max(10, min(400, min_ms / max(float(first.item()), 1e-3))))
+    before = lib.ff_topk_launch_count()
+    times = []
+    for _ in range(n_rep):
+        # barrier + synchronize on both sides of every timed replay; device time, max over ranks below
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        times.append(one_replay())
+    dist.barrier()
+    if graph is None:
+        launches = (lib.ff_topk_launch_count() - before) // max(n_rep, 1)
+    t = torch.tensor(times, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) * 1e3 / K for x in t.tolist()], graph is not None, int(launches)
+
+
+def _cp_parity(plan, shard_of, row_ids, lengths, k, world, rank, dist, dev, hint=None):
+    """Outside any timed region: for each row id, the context-parallel result of every rank is
+    compared with the one-GPU operator on the gathered row (that path is checked against the CPU
+    oracle by the parity tests, at these sizes too).  Returns the number of rows compared; raises
+    on any mismatch on any rank."""
+    from flash_float_jit_kernels_b200 import fast_topk_v3
+    bad = torch.zeros(1, dtype=torch.int32, device=dev)
+    n = 0
+    for i in row_ids:
+        shard = shard_of(i)
+        got = plan(shard, lengths, shard_of.offset, threshold_hint=hint).clone()
+        parts = [torch.empty_like(shard) for _ in range(world)]
+        dist.all_gather(parts, shard.contiguous())
+        row = torch.cat(parts, dim=1)
+        want = fast_topk_v3(row, lengths, k)
+        torch.cuda.synchronize()
+        if rank == 0:
+            check_selection(row[0], want[0], k)
+        if not torch.equal(got, want):
+            bad += 1
+        n += 1
+    dist.all_reduce(bad, op=dist.ReduceOp.SUM)
+    plan.check_status()
+    if int(bad.item()) != 0:
+        raise SystemExit(f"bench: context-parallel result differs from the one-GPU result "
+                         f"({int(bad.item())} rank-rows of {n * world})")
+    return n
+
+
+class _Shards:
+    """Callable row id -> this rank's (1, L_local) shard, with the shard's first global column."""
+
+    def __init__(self, shards, offset):
+        self.shards, self.offset = shards, offset
+
+    def __call__(self, i):
+        return self.shards[i % self.shards.shape[0]].unsqueeze(0)
+
+
 def bench_cp(args):
     import torch.distributed as dist
-    from flash_float_jit_kernels_b200 import _lib
+    from flash_float_jit_kernels_b200 import _lib, fast_topk_v3, new_threshold_hint, shard_bounds
     from flash_float_jit_kernels_b200.context_parallel import ContextParallelTopk
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -449,87 +617,46 @@ def bench_cp(args):
     K, W = args.steps, max(args.warmup, 3)
     L, k = L_SHARD * world, K_TOP
     n_rot = 32
-    shards = make_rows(n_rot, L_SHARD, dev, seed=1000 + rank)       # this rank's columns of 32 distinct rows
+    shards = _Shards(make_rows(n_rot, L_SHARD, dev, seed=1000 + rank), rank * L_SHARD)   # this rank's columns of 32 rows
     lengths = torch.tensor([L], dtype=torch.int32, device=dev)
     plan = ContextParallelTopk(1, k, dev, exchange=args.exchange)
-    offset = rank * L_SHARD
 
-    hint = None
-    if args.threshold_hint:                                          # secondary measurement, not the default line
-        from flash_float_jit_kernels_b200 import new_threshold_hint
-        hint = new_threshold_hint(1, dev)
+    hint = new_threshold_hint(1, dev) if args.threshold_hint else None   # secondary measurement, not the default line
 
     def step(i):
-        return plan(shards[i % n_rot].unsqueeze(0), lengths, offset, threshold_hint=hint)
+        return plan(shards(i), lengths, shards.offset, threshold_hint=hint)
 
     for i in range(W):
         step(i)
     torch.cuda.synchronize()
     dist.barrier()
-    # With the peer-memory exchange a step is one kernel launch and no library call, so the
-    # K steps are captured into one CUDA graph (the step counter lives in device memory);
-    # with the NCCL exchange they are launched eagerly.
-    graph = None
-    side = torch.cuda.Stream()
-    if plan.exchange == "p2p" and not args.no_graph:
-        try:
-            with torch.cuda.stream(side):
-                before_cap = lib.ff_topk_launch_count()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    for i in range(K):
-                        step(i)
-                launches_per_replay = lib.ff_topk_launch_count() - before_cap
-            graph = g
-        except Exception:
-            graph = None
-    ok = torch.tensor([1 if graph is not None else 0], device=dev)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)           # all ranks replay a graph, or none does
-    if int(ok.item()) == 0:
-        graph = None
-    if graph is not None:
-        with torch.cuda.stream(side):
-            graph.replay()                                  # untimed: upload + warm-up
-        side.synchronize()
-    before = lib.ff_topk_launch_count()
+    # ---- parity on real ranks, before anything is timed: plain steps and steps with guesses ----
+    rows_checked = _cp_parity(plan, shards, range(4), lengths, k, world, rank, dist, dev)
+    hint_chk = new_threshold_hint(1, dev)
+    rows_checked += _cp_parity(plan, shards, [0, 0, 1, 2], lengths, k, world, rank, dist, dev, hint=hint_chk)
+
     sampler = ClockSampler(local)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
     t0 = time.perf_counter()
-    if graph is not None:
-        with torch.cuda.stream(side):
-            e0.record(side)
-            graph.replay()
-            e1.record(side)
-        side.synchronize()
-    else:
-        e0.record()
-        for i in range(K):
-            step(i)
-        e1.record()
-    torch.cuda.synchronize()
+    samples, graphed, launches = _cp_time(plan, step, K, lib, args, dist, dev)
     t1 = time.perf_counter()
-    dist.barrier()
-    launches = launches_per_replay if graph is not None else lib.ff_topk_launch_count() - before
-    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     clocks = sampler.summary(t0, t1)
     sampler.stop()
-    us = float(ms.item()) * 1e3 / K
+    q = quantiles(samples)
+    us = q["p50"]
+    q["mean"] = round(sum(samples) / len(samples), 3)
+    plan.check_status()
 
-    # end to end with host shards
+    # ---- end to end with host shards ----------------------------------------
     host_in = torch.empty((1, L_SHARD), dtype=torch.float32).pin_memory()
-    host_in.copy_(shards[0:1].cpu())
+    host_in.copy_(shards(0).cpu())
     host_out = torch.empty((1, k), dtype=torch.int32).pin_memory()
     dev_in = torch.empty((1, L_SHARD), dtype=torch.float32, device=dev)
-    Ke = min(K, 200)
+    Ke = 200
 
     def e2e_step():
         dev_in.copy_(host_in, non_blocking=True)
-        o = plan(dev_in, lengths, offset)
+        o = plan(dev_in, lengths, shards.offset)
         host_out.copy_(o, non_blocking=True)
 
     for _ in range(3):
@@ -537,6 +664,7 @@ def bench_cp(args):
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(Ke):
         e2e_step()
@@ -546,6 +674,52 @@ def bench_cp(args):
     ems = torch.tensor([e0.elapsed_time(e1)], device=dev)
     dist.all_reduce(ems, op=dist.ReduceOp.MAX)
     e2e_us = float(ems.item()) * 1e3 / Ke
+    plan.check_status()
+
+    # ---- the long-context configuration as stated: fp32 N(0,1), L = 4 Mi and 8 Mi over the N ranks,
+    # beside one GPU (rank 0) on the same rows -----------------------------------------------------
+    c5 = {}
+    if not args.no_extra:
+        for Lc in (1 << 22, 1 << 23):
+            a, b = shard_bounds(Lc, world, rank)
+            n_rows = max(4, min(64, (160 << 20) // (4 * (b - a)) + 1))      # this rank's shards exceed L2
+            n_full = max(4, (160 << 20) // (4 * Lc) + 1) if rank == 0 else 0
+            g = torch.Generator(device=dev)
+            g.manual_seed(5000 + Lc)                                        # same rows on every rank
+            full, mine = [], []
+            for i in range(n_rows):
+                row = torch.randn((Lc,), generator=g, device=dev, dtype=torch.float32)
+                mine.append(row[a:b].clone())
+                if i < n_full:
+                    full.append(row)
+            sh = _Shards(torch.stack(mine), a)
+            len_c = torch.tensor([Lc], dtype=torch.int32, device=dev)
+            for i in range(3):
+                plan(sh(i), len_c, a)
+            checked = _cp_parity(plan, sh, range(3), len_c, k, world, rank, dist, dev)
+            rows_checked += checked
+            cs, _, _ = _cp_time(plan, lambda i: plan(sh(i), len_c, a), K, lib, args, dist, dev, min_ms=20.0)
+            cq = quantiles(cs)
+            hint_c = new_threshold_hint(1, dev)
+            for i in range(3):
+                plan(sh(i), len_c, a, threshold_hint=hint_c)
+            hs, _, _ = _cp_time(plan, lambda i: plan(sh(i), len_c, a, threshold_hint=hint_c), K, lib, args, dist, dev,
+                                min_ms=20.0)
+            us_1gpu = None
+            if rank == 0:
+                fullt = torch.stack(full)
+                o1 = torch.empty((1, k), dtype=torch.int32, device=dev)
+                us_1gpu = _time_calls(lambda i: fast_topk_v3(fullt[i:i + 1], len_c, k, out=o1), len(full), 100, dev)
+                del fullt
+            dist.barrier()
+            if rank == 0:
+                c5[str(Lc)] = {"us_1gpu": round(us_1gpu, 2), "us_cp": cq["p50"], "us_cp_quantiles": cq,
+                               "speedup": round(us_1gpu / cq["p50"], 3),
+                               "us_cp_threshold_hint": quantiles(hs)["p50"],
+                               "shard_columns": b - a, "rows_parity_checked": checked,
+                               "data": "fp32 N(0,1), same seeded rows on every rank"}
+            del full, mine, sh
+        plan.check_status()
 
     if rank == 0:
         peak, peak_src = measured_peak()
@@ -555,25 +729,28 @@ def bench_cp(args):
             "metric": "topk_us_per_call", "value": round(us, 3), "unit": "us", "n_gpus": world, "steps": K,
             "warmup": W, "ms_per_step": round(us / 1e3, 6), "higher_is_better": False, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32->u32 keys", "data": "synthetic",
+            "quantiles": q, "parity_checked": True, "parity_rows_compared": rows_checked,
             "config": {"workload": f"context-parallel B=1 L={L} k=2048 bf16-rounded N(0,1), "
                                    f"{world} contiguous shards of {L_SHARD} columns",
                        "B": 1, "L": L, "k": k, "parallelism": f"cp{world}",
                        "threshold_hint": bool(args.threshold_hint),
                        "l2": f"each rank rotates over {n_rot} distinct 4 MiB shards (128 MiB > 126 MB L2)",
-                       "timing": ("K steps in one CUDA graph replay" if graph is not None else
-                                  "eager stream launches") + ", CUDA events, max over ranks",
-                       "exchange": ("self-validating 16-byte entries stored into every peer's receive buffer "
-                                    "over NVLink from the select kernel (32 KiB per rank per peer); the same "
-                                    "launch polls its local entries and merges" if plan.exchange == "p2p" else
-                                    "NCCL all-gather of (value, global index) candidates, 16 KiB per rank")},
+                       "timing": (f"K steps in one CUDA graph replay" if graphed else "K eager stream launches") +
+                                 f", {len(samples)} replays each between barriers, CUDA events, max over ranks per "
+                                 "replay, value = median per-step time",
+                       "parity": "every rank's result of 8 steps (4 plain, 4 with threshold guesses) and of 3 steps "
+                                 "per long-context row length equals the one-GPU operator on the gathered row",
+                       "exchange": plan.describe_exchange()},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak * world, "unit": "GB/s",
                          "frac": round(achieved / (peak * world), 5), "traffic": None, "peak_source": peak_src,
                          "algorithmic_bytes_per_launch": algo_bytes,
-                         "note": "whole step (select + exchange + merge) against N x the HBM peak"},
+                         "note": "whole step (select + exchange + merge) against N x the HBM peak; no ncu capture "
+                                 "of a multi-rank step is taken (ncu is never wrapped around several ranks)"},
             "e2e": {"value": round(e2e_us, 3), "unit": "us", "h2d_bytes_per_step": 4 * L_SHARD,
                     "d2h_bytes_per_step": 4 * k, "steps": Ke},
             "gpu_launches": int(launches),
             "clocks": clocks,
+            "extra": {"c5": c5},
         }
         print(json.dumps(line))
     plan.close()

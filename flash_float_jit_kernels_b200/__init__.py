@@ -11,7 +11,12 @@ from .topk_indexer import (  # noqa: F401
     fast_topk_transform_ragged_fused,
     new_threshold_hint,
 )
-from .context_parallel import fast_topk_v3_cp, shard_bounds  # noqa: F401
+from .context_parallel import (  # noqa: F401
+    ContextParallelTopk,
+    close_cached_plans,
+    fast_topk_v3_cp,
+    shard_bounds,
+)
 
 __all__ = [
     "TopkArgumentError",
@@ -20,5 +25,7 @@ __all__ = [
     "fast_topk_transform_ragged_fused",
     "new_threshold_hint",
     "fast_topk_v3_cp",
+    "ContextParallelTopk",
+    "close_cached_plans",
     "shard_bounds",
 ]

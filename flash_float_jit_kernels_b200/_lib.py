@@ -22,6 +22,7 @@ SIGNATURES = {
     "ff_topk_set_trace_buffer": (c_int, [c_void_p]),
     "ff_topk_set_groups_override": (c_int, [c_int32]),
     "ff_topk_policy_cluster_size": (c_int32, [c_int32, c_int64, c_int32]),
+    "ff_topk_policy_launch_shape": (c_int, [c_int32, c_int64, c_int32, c_int32, c_int32, ctypes.POINTER(c_int32)]),
     "ff_topk_workspace_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
     "ff_topk_launch": (
         c_int,
@@ -85,6 +86,7 @@ FF_EPILOGUE_INDEX = 0
 FF_EPILOGUE_PAGE_TABLE = 1
 FF_EPILOGUE_ADD_OFFSET = 2
 FF_TOPK_MAX_K = 2048
+FF_STATUS_WAIT_TIMEOUT = 2
 FF_STATUS_HINT_MISSED = 8
 
 

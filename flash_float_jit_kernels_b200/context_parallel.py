@@ -73,6 +73,8 @@ class ContextParallelTopk:
                 self.exchange = "p2p"
             elif exchange == "p2p":
                 raise RuntimeError("peer-memory exchange could not be set up on every rank")
+        # Soft-error bits of every step accumulate here (the kernels OR into it); see check_status().
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         # plane 0: value bits, plane 1: global index
         self.send = torch.empty((2, B, topk), dtype=torch.int32, device=self.device)
         self.recv = torch.empty((self.world, 2, B, topk), dtype=torch.int32, device=self.device)
@@ -107,13 +109,63 @@ class ContextParallelTopk:
         return True
 
     def close(self) -> None:
-        """Releases the peer mappings and buffers (collective: every rank calls it)."""
+        """Releases the peer mappings and buffers (collective: every rank calls it, so that no
+        rank unmaps a buffer a peer's kernel may still store into)."""
         if self._ex is not None:
             torch.cuda.synchronize(self.device)
-            if self.world > 1:
+            if self.world > 1 and dist.is_initialized():
                 dist.barrier(group=self.group)
-            _lib.load().ff_cp_exchange_destroy(self._ex)
-            self._ex = None
+            self._release()
+
+    def _release(self) -> None:
+        """Non-collective release of this rank's exchange allocation and peer mappings."""
+        ex, self._ex = self._ex, None
+        if ex is not None:
+            try:
+                _lib.load().ff_cp_exchange_destroy(ex)
+            except Exception:     # interpreter shutdown: the driver reclaims the memory with the process
+                pass
+
+    def __enter__(self) -> "ContextParallelTopk":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    def __del__(self):
+        # A plan that was never closed must not leak its allocation.  No barrier is possible in a
+        # finalizer, so only this rank's side is released, after its own work has drained; peers
+        # that are still stepping would fault, which is why close() is the documented way out.
+        if getattr(self, "_ex", None) is not None:
+            try:
+                torch.cuda.synchronize(self.device)
+            except Exception:
+                pass
+            self._release()
+
+    def describe_exchange(self) -> str:
+        """One line saying how candidates travel between the ranks (for benchmark records)."""
+        if self.exchange == "p2p":
+            return ("self-validating 16-byte entries stored into every peer's receive buffer over NVLink from "
+                    "the select kernel; the same launch polls its local entries and merges")
+        return "NCCL all-gather of (value, global index) candidates, 16 KiB per rank"
+
+    def check_status(self, reset: bool = True) -> int:
+        """Reads the accumulated soft-error bits (this synchronises the device, so call it at a
+        point of your choosing, not per step).  ``FF_STATUS_WAIT_TIMEOUT`` (2) means a peer's
+        entries did not arrive within the bounded wait: the affected step's result is INVALID
+        (slots it could not fill keep older contents) and the ranks may be more than one step
+        apart, which the two alternating receive buffers do not cover.  Before stepping again,
+        re-synchronise every rank (a host barrier with all streams drained) or build a new plan.
+        Raises ``RuntimeError`` on that bit; returns the other bits (information only)."""
+        bits = int(self.status.item())
+        if reset and bits:
+            self.status.zero_()
+        if bits & _lib.FF_STATUS_WAIT_TIMEOUT:
+            raise RuntimeError(
+                "context-parallel top-k: a bounded wait ran out (FF_STATUS_WAIT_TIMEOUT): a result since the "
+                "last check is invalid; re-synchronise all ranks (barrier) or re-create the plan before the next step")
+        return bits
 
     def _step_p2p(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int,
                   threshold_hint: Optional[torch.Tensor] = None) -> None:
@@ -124,8 +176,8 @@ class ContextParallelTopk:
         with torch.cuda.device(score_shard.device):
             rc = lib.ff_topk_cp_step_hinted(
                 self._ex, score_shard.data_ptr(), score_shard.stride(0) if B > 1 else max(score_shard.stride(0), L),
-                lengths.data_ptr(), self.out.data_ptr(), L, shard_offset, hint, hint, _ptr(ws), ws_bytes, None,
-                _stream_ptr(score_shard.device))
+                lengths.data_ptr(), self.out.data_ptr(), L, shard_offset, hint, hint, _ptr(ws), ws_bytes,
+                self.status.data_ptr(), _stream_ptr(score_shard.device))
         _lib.check(rc, "ff_topk_cp_step_hinted")
 
     # -- step 1 ---------------------------------------------------------
@@ -137,7 +189,8 @@ class ContextParallelTopk:
             rc = lib.ff_topk_cp_local(
                 score_shard.data_ptr(), score_shard.stride(0) if B > 1 else max(score_shard.stride(0), L),
                 lengths.data_ptr(), self.send[1].data_ptr(), self.send[0].data_ptr(),
-                B, L, self.k, shard_offset, _ptr(ws), ws_bytes, None, _stream_ptr(score_shard.device))
+                B, L, self.k, shard_offset, _ptr(ws), ws_bytes, self.status.data_ptr(),
+                _stream_ptr(score_shard.device))
         _lib.check(rc, "ff_topk_cp_local")
 
     # -- step 2 ---------------------------------------------------------
@@ -156,7 +209,7 @@ class ContextParallelTopk:
             rc = lib.ff_topk_cp_merge(
                 self.recv[0, 0].data_ptr(), self.recv[0, 1].data_ptr(), self.world,
                 2 * self.B * self.k, lengths.data_ptr(), self.out.data_ptr(), self.B, self.k,
-                _ptr(ws), ws_bytes, None, _stream_ptr(self.device))
+                _ptr(ws), ws_bytes, self.status.data_ptr(), _stream_ptr(self.device))
         _lib.check(rc, "ff_topk_cp_merge")
 
     def __call__(self, score_shard: torch.Tensor, lengths: torch.Tensor, shard_offset: int,
@@ -186,6 +239,9 @@ class ContextParallelTopk:
         return self.out
 
 
+_PLANS: dict = {}
+
+
 def fast_topk_v3_cp(
     score_shard: torch.Tensor,
     lengths: torch.Tensor,
@@ -194,9 +250,22 @@ def fast_topk_v3_cp(
     group=None,
     plan: Optional[ContextParallelTopk] = None,
 ) -> torch.Tensor:
-    """Functional form of :class:`ContextParallelTopk` (allocates its buffers
-    per call unless ``plan`` is passed)."""
+    """Functional form of :class:`ContextParallelTopk`.  Without ``plan`` the plan for this
+    (device, group, B, topk) is built on first use (a collective: every rank must make the same
+    first call) and kept for later calls, so a per-step call allocates nothing; release the kept
+    plans with :func:`close_cached_plans`."""
     _check_common(score_shard, lengths, topk, None)
     if plan is None:
-        plan = ContextParallelTopk(score_shard.size(0), topk, score_shard.device, group)
+        key = (score_shard.device, id(group) if group is not None else None, score_shard.size(0), topk)
+        plan = _PLANS.get(key)
+        if plan is None:
+            plan = ContextParallelTopk(score_shard.size(0), topk, score_shard.device, group)
+            _PLANS[key] = plan
     return plan(score_shard, lengths, shard_offset)
+
+
+def close_cached_plans() -> None:
+    """Closes the plans :func:`fast_topk_v3_cp` keeps (collective, like ``ContextParallelTopk.close``)."""
+    while _PLANS:
+        _, plan = _PLANS.popitem()
+        plan.close()

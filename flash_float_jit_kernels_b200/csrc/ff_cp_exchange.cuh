@@ -5,10 +5,10 @@
 // {value bits, step, global index, step}.  The shard-local select kernel stores
 // each of its k candidates per row straight into EVERY peer's slot as it ranks
 // them, one 16-byte store per candidate and peer (the link carries one packet
-// per store, so fewer and wider stores matter at 8 ranks).  An 8-byte aligned
-// half arrives whole, so the step number inside each half is its own "valid"
-// mark: the receiver polls a half until it carries the current step (bounded
-// wait).  No fence, no flag, no collective library call; the
+// per store, so fewer and wider stores matter at 8 ranks).  Each half is one
+// 64-bit word (payload low, step high) and a 64-bit access is single-copy
+// atomic, so the step number inside each half is its own "valid" mark: the
+// receiver polls a half until it carries the current step (bounded wait).  No fence, no flag, no collective library call; the
 // receiver reads local memory only.
 // The reference has no multi-GPU path; semantics follow fast_topk_v3
 // (jit_kernel/topk_indexer.py:109) on the unsharded row.
@@ -44,14 +44,18 @@ __device__ __forceinline__ uint32_t run_key_of_bits(uint32_t bits) {
   return bits == kNoCandidateBits ? 0u : key_of_bits(bits);
 }
 
+// An entry is two 64-bit words, {value bits | step << 32} and {global index | step << 32}.  A 64-bit
+// scalar access is single-copy atomic in the PTX memory model, so a reader that sees the current
+// step in a word's high half also sees that word's payload: each word validates itself.
 __device__ __forceinline__ void st_entry(uint32_t* entry, uint32_t value_bits, uint32_t gidx, uint32_t step) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(entry), "r"(value_bits), "r"(step), "r"(gidx)
+  const unsigned long long hi = static_cast<unsigned long long>(step) << 32;
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(entry), "l"(hi | value_bits), "l"(hi | gidx)
                : "memory");
 }
 __device__ __forceinline__ uint2 ld_entry(const uint32_t* entry) {
-  uint2 e;
-  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(entry) : "memory");
-  return e;
+  unsigned long long w;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(entry) : "memory");
+  return make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
 }
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;

@@ -203,7 +203,10 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   attr[1].id = cudaLaunchAttributeCooperative;
   attr[1].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = groups > 1 ? 2 : 1;
+  // Cooperative whenever CTAs of the launch wait for each other through global memory: rows split
+  // over clusters, and the single-kernel context-parallel step (its CTAs poll for entries that
+  // CTAs of the same launch on the peers store), so that residency is guaranteed, not inferred.
+  cfg.numAttrs = (groups > 1 || p.push_fused != 0) ? 2 : 1;
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
 
@@ -228,16 +231,30 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
 // library until the process exits.  In host code the name below is only a
 // handle for cudaGetSymbolAddress; it is never passed to a kernel.
 static __device__ __align__(256) uint32_t g_static_scratch[FF_TOPK_STATIC_MAX_ROWS * ff::kWsRowWords];
-std::once_flag g_static_once[kMaxDevices];
-int g_static_rc[kMaxDevices];
-uint32_t* g_static_ptr[kMaxDevices];
+std::mutex g_static_mutex;
+std::atomic<uint32_t*> g_static_ptr[kMaxDevices];
 
-// Runs once per device, with that device current.
-void resolve_static_scratch(int device) {
-  void* ptr = nullptr;
-  const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
-  g_static_rc[device] = static_cast<int>(e);
-  g_static_ptr[device] = e == cudaSuccess ? static_cast<uint32_t*>(ptr) : nullptr;
+// Device address of the built-in scratch on `device`, which must be current.  Only a success is
+// remembered: a first call that fails (for instance because it was made while a stream capture
+// was active) leaves nothing behind, and the next call simply tries again.
+int static_scratch_address(int device, uint32_t** out) {
+  uint32_t* ptr = g_static_ptr[device].load(std::memory_order_acquire);
+  if (ptr == nullptr) {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    ptr = g_static_ptr[device].load(std::memory_order_relaxed);
+    if (ptr == nullptr) {
+      void* sym = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&sym, g_static_scratch);
+      if (e != cudaSuccess || sym == nullptr) {
+        (void)cudaGetLastError();
+        return fail_cuda(e == cudaSuccess ? cudaErrorInvalidSymbol : e, "cudaGetSymbolAddress(built-in scratch)");
+      }
+      ptr = static_cast<uint32_t*>(sym);
+      g_static_ptr[device].store(ptr, std::memory_order_release);
+    }
+  }
+  *out = ptr;
+  return 0;
 }
 
 int check_common(int32_t B, int64_t L_width, int32_t k) {
@@ -283,6 +300,21 @@ int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k) {
   int device = 0;
   if (ensure_init(&device) != 0) return -1;
   return choose_cluster(device, B, L_width, k);
+}
+
+int ff_topk_policy_launch_shape(int32_t B, int64_t L_width, int32_t k, int32_t has_workspace, int32_t hinted,
+                                int32_t* out2) {
+  if (out2 == nullptr) return fail(FF_ERR_NULL, "out2 must not be NULL");
+  int device = 0;
+  const int rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  int cluster = choose_cluster(device, B, L_width, k);
+  int groups = 1;
+  if (has_workspace != 0)
+    groups = choose_groups(device, B, L_width, ff_topk_workspace_bytes(B, L_width, k), &cluster, hinted != 0);
+  out2[0] = cluster;
+  out2[1] = groups;
+  return 0;
 }
 
 size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
@@ -405,14 +437,10 @@ int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t
   int device = 0;
   rc = ensure_init(&device);
   if (rc != 0) return rc;
-  std::call_once(g_static_once[device], resolve_static_scratch, device);
-  if (g_static_rc[device] != 0 || g_static_ptr[device] == nullptr)
-    return fail_cuda(static_cast<cudaError_t>(g_static_rc[device]), "cudaGetSymbolAddress(built-in scratch)");
-  uint32_t* scratch = g_static_ptr[device];
+  uint32_t* scratch = nullptr;
+  rc = static_scratch_address(device, &scratch);
+  if (rc != 0) return rc;
   const size_t row_bytes = static_cast<size_t>(ff::kWsRowWords) * sizeof(uint32_t);
-  // The array keeps whatever the previous call left; the counters and histograms must start at zero.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, static_cast<size_t>(B) * row_bytes, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(built-in scratch)");
   ff::TopkParams p = {};
   p.scores = scores;
   p.row_stride = row_stride;
@@ -428,6 +456,13 @@ int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t
   int cluster = choose_cluster(device, B, L_width, k);
   p.groups = choose_groups(device, B, L_width, FF_TOPK_STATIC_MAX_ROWS * row_bytes, &cluster);
   p.workspace = scratch;
+  if (p.groups > 1) {
+    // Only rows split over several clusters touch the scratch.  The array keeps whatever the
+    // previous call left; the counters, histograms and lists must start at zero.
+    const cudaError_t e =
+        cudaMemsetAsync(scratch, 0, static_cast<size_t>(B) * row_bytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync(built-in scratch)");
+  }
   return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
 }
 

@@ -648,6 +648,9 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
     }
     if (two_step) {
       const int lane = tid & 31;
+      // release side of the hand-over: the lane that publishes a coarse sum fences first, after the
+      // CTA barrier that ordered every thread's fine-bin additions before it
+      if (self_counting && lane == 0) __threadfence();
       for (int g = tid >> 5; g < slice_n / 32; g += kWarps) {
         const uint32_t sum = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(slice_at(32 * g + lane)));
         if (lane == 0 && sum != 0u) atomicAdd(ws + kWsCoarseWord + slice_base / 32 + g, sum);
@@ -663,7 +666,9 @@ __device__ __forceinline__ void merge_and_scan(cg::cluster_group& cluster, int C
         bool complete = false;
         for (int spin = 0; spin < (kSpinLimit >> 6) && !complete; ++spin) {
           uint32_t w = 0u;
-          if (tid < 256) asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(w) : "l"(ws + kWsCoarseWord + tid) : "memory");
+          // acquire: a complete coarse sum makes the fine bins added before it visible (the CTA
+          // barriers of the scan below carry that on to the lanes that read the fine bins)
+          if (tid < 256) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(w) : "l"(ws + kWsCoarseWord + tid) : "memory");
           val = static_cast<int>(w);
           excl = block_suffix_exclusive(val, sh.warp_tot, total);
           complete = total == counted;

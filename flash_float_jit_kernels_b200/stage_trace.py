@@ -41,7 +41,10 @@ def trace_once(score, lengths, k, cluster=0, hinted=False):
     lib = _lib.load()
     dev = score.device
     lib.ff_topk_set_cluster_override(cluster)
-    C = lib.ff_topk_policy_cluster_size(score.shape[0], score.shape[1], k)
+    import ctypes
+    shape = (ctypes.c_int32 * 2)()
+    lib.ff_topk_policy_launch_shape(score.shape[0], score.shape[1], k, 1, 1 if hinted else 0, shape)
+    C = int(shape[0])            # CTAs per cluster of the launch actually made (a row may span shape[1] clusters)
     # a row may be split over up to 64 clusters of up to 16 CTAs: size the buffer for the largest grid
     buf = torch.zeros((score.shape[0] * 1024, 32), dtype=torch.int64, device=dev)
     out = torch.empty((score.shape[0], k), dtype=torch.int32, device=dev)

@@ -83,40 +83,40 @@ def lightning_indexer_logits(B: int, L_max: int, min_len: int, seed: int = 2, de
 
 
 # ---- the reference benchmark's distributions, scaled to [0, 255] -----------
-def _minmax(x):
-    lo, hi = x.min(), x.max()
-    return (x - lo) / (hi - lo)
-
-
 def _ref_unit(dist: str, n: int, g: torch.Generator, device) -> torch.Tensor:
-    def randn(m=n):
-        return torch.randn((m,), generator=g, device=device, dtype=torch.float32)
+    """The seven [0, 1] score distributions of the reference benchmark, with its parameters
+    (``benchmark/bench_topk.py:60-96``), drawn from a seeded generator instead of the global one."""
+    def randn():
+        return torch.randn((n,), generator=g, device=device, dtype=torch.float32)
 
-    def rand(m=n):
-        return torch.rand((m,), generator=g, device=device, dtype=torch.float32)
+    def rand():
+        return torch.rand((n,), generator=g, device=device, dtype=torch.float32)
 
-    if dist == "gaussian":
-        return _minmax(randn())
-    if dist == "uniform":
+    if dist == "gaussian":      # randn normalised by its own range (+1e-6), bench_topk.py:86-89
+        x = randn()
+        return (x - x.min()) / (x.max() - x.min() + 1e-6)
+    if dist == "uniform":       # bench_topk.py:60-61
         return rand()
-    if dist == "sigmoid":
-        return torch.sigmoid(randn() * 2.0)
-    if dist == "beta":
-        # Beta(.5,.5) by the arcsine law: sin^2(pi/2 * U)
-        return torch.sin(rand() * (math.pi / 2)) ** 2
-    if dist == "power":
+    if dist == "sigmoid":       # sigmoid of a standard normal, bench_topk.py:64-66
+        return torch.sigmoid(randn())
+    if dist == "beta":          # Beta(0.5, 0.5), bench_topk.py:69-71; drawn by the arcsine law sin^2(pi/2 U),
+        return torch.sin(rand() * (math.pi / 2)) ** 2      # which has exactly that distribution
+    if dist == "power":         # U^6, bench_topk.py:74-76
         return rand() ** 6
-    if dist == "bimodal":
+    if dist == "bimodal":       # half uniform on [0, 0.25], half uniform on [0.75, 1], bench_topk.py:79-83
         pick = rand() < 0.5
-        return torch.where(pick, 0.2 + 0.05 * randn(), 0.8 + 0.05 * randn())
-    if dist == "sparse":
-        x = rand() * 0.05
+        return torch.where(pick, 0.25 * rand(), 0.75 + 0.25 * rand())
+    if dist == "sparse":        # 2 % spikes uniform on [0.5, 1], background uniform on [0, 0.01], bench_topk.py:92-96
         hot = rand() < 0.02
-        return torch.where(hot, 0.5 + 0.5 * rand(), x)
+        return torch.where(hot, 0.5 + 0.5 * rand(), 0.01 * rand())
     raise ValueError(dist)
 
 
 REFERENCE_DISTRIBUTIONS = ("gaussian", "uniform", "sigmoid", "beta", "power", "bimodal", "sparse")
+# the reference benchmark's grid (bench_topk.py:418-431): every combination, each with and without row_starts
+REFERENCE_GRID_BS = (1, 2, 4, 8)
+REFERENCE_GRID_K = (512, 1024, 2048)
+REFERENCE_GRID_SEQ_LEN = (16384, 65536, 98304, 120000)
 
 
 def reference_style(B: int, seq_len: int, has_row_starts: bool, dist: str = "uniform",

@@ -95,11 +95,13 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
  * loading the library holds until the process exits.
  *   - B > FF_TOPK_STATIC_MAX_ROWS is rejected with FF_ERR_TOO_LARGE.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine; it
- *     enqueues one cudaMemsetAsync (the scratch keeps the previous call's
- *     contents and its counters must start at zero) and one kernel on `stream`.
+ *     enqueues one kernel on `stream`, preceded by one cudaMemsetAsync when the
+ *     rows are long enough to use the scratch (the array keeps the previous
+ *     call's contents and its counters must start at zero).
  *   - The first call on each device resolves the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call
- *     before starting any stream capture.
+ *     before starting any stream capture.  Only a successful look-up is kept:
+ *     if it fails, the call returns the error and the next call tries again.
  *   - All calls on one GPU share the one array: two calls that can overlap on
  *     the GPU (different streams) race on it and give wrong results. */
 #define FF_TOPK_STATIC_MAX_ROWS 4
@@ -227,8 +229,18 @@ int ff_topk_set_trace_buffer(void* device_buffer);
 int ff_topk_set_groups_override(int32_t groups);
 
 /* The cluster size the automatic policy picks for (B, L_width, k) on the
- * current device (after overrides). */
+ * current device (after overrides) when a row stays inside ONE cluster (no
+ * workspace).  For the shape of an actual launch use ff_topk_policy_launch_shape. */
 int32_t ff_topk_policy_cluster_size(int32_t B, int64_t L_width, int32_t k);
+
+/* The launch shape ff_topk_launch (hinted == 0) or ff_topk_launch_hinted
+ * (hinted != 0) uses for (B, L_width, k) on the current device: out2[0] = CTAs
+ * per cluster, out2[1] = clusters per row (more than one only with workspace of
+ * ff_topk_workspace_bytes; pass has_workspace = 0 for a call without).  The
+ * grid is B * out2[0] * out2[1] CTAs.  Plays the role of reading the reference's
+ * split policy off its launcher (topk_indexer_radix.cu:1309-1321). */
+int ff_topk_policy_launch_shape(int32_t B, int64_t L_width, int32_t k, int32_t has_workspace, int32_t hinted,
+                                int32_t* out2);
 
 /* Number of kernel launches issued through this library since load
  * (all threads); used by the benchmark's launch accounting. */

@@ -259,6 +259,40 @@ def test_single_kernel_step_with_a_missing_peer_times_out():
             lib.ff_cp_exchange_destroy(h)
 
 
+def test_plan_wrapper_surfaces_a_missing_peer_as_an_exception(oracle):
+    """The Python plan passes its own status word to every step: a step whose peer never
+    delivers ends by its bounded wait, and check_status() raises instead of returning stale
+    indices silently.  (The peer is a second exchange on this GPU that is never stepped.)"""
+    import ctypes
+    from flash_float_jit_kernels_b200 import _lib
+    from flash_float_jit_kernels_b200.context_parallel import ContextParallelTopk
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    B, L, k = 1, 50000, 256
+
+    class TwoRankPlanWithSilentPeer(ContextParallelTopk):
+        def _setup_p2p(self):
+            self.world, self.rank = 2, 0
+            self._both = _make_exchanges(lib, 2, B, k)
+            self._ex = self._both[0]
+            return True
+
+    plan = TwoRankPlanWithSilentPeer(B, k, dev, exchange="p2p")
+    try:
+        s = torch.randn((B, L), device=dev)
+        lengths = torch.tensor([2 * L], dtype=torch.int32, device=dev)
+        plan(s, lengths, 0)
+        with pytest.raises(RuntimeError, match="FF_STATUS_WAIT_TIMEOUT"):
+            plan.check_status()
+        assert plan.check_status() == 0, "the bits were cleared by the failed check"
+        assert float(torch.ones(4, device=dev).sum()) == 4.0           # context still usable
+    finally:
+        torch.cuda.synchronize()
+        plan._ex = None
+        for h in plan._both:
+            lib.ff_cp_exchange_destroy(h)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("P,L", [(2, 600000), (4, 2400000)])
 def test_peer_exchange_with_threshold_guesses(oracle, P, L):

@@ -56,3 +56,20 @@ def test_reference_import_path_shim(monkeypatch):
     assert shim is pkg.fast_topk_v3
     sys.modules.pop("jit_kernel", None)
     sys.modules.pop("jit_kernel.topk_indexer", None)
+
+
+def test_cp_plan_status_surfaces_a_timeout_and_plan_is_a_context_manager():
+    """The plan keeps one status word for all its steps; bit 2 (a bounded wait ran out) turns into
+    an exception at the caller's sync point, other bits are returned and cleared."""
+    from flash_float_jit_kernels_b200 import _lib
+    from flash_float_jit_kernels_b200.context_parallel import ContextParallelTopk
+    with ContextParallelTopk(2, 16, torch.device("cpu"), exchange="nccl") as plan:
+        assert plan.check_status() == 0
+        plan.status.fill_(_lib.FF_STATUS_HINT_MISSED)
+        assert plan.check_status() == _lib.FF_STATUS_HINT_MISSED
+        assert int(plan.status.item()) == 0, "read bits are cleared"
+        plan.status.fill_(_lib.FF_STATUS_WAIT_TIMEOUT | _lib.FF_STATUS_HINT_MISSED)
+        with pytest.raises(RuntimeError, match="re-synchronise"):
+            plan.check_status()
+        assert int(plan.status.item()) == 0
+    assert plan._ex is None

@@ -87,12 +87,26 @@ def test_config5_long_rows_single_gpu(ff, oracle, L):
 
 @pytest.mark.parametrize("dist", ["gaussian", "uniform", "sigmoid", "beta", "power", "bimodal", "sparse"])
 @pytest.mark.parametrize("has_rs", [False, True])
-def test_reference_benchmark_grid(ff, oracle, dist, has_rs):
-    # benchmark/bench_topk.py:418-431 grid (a subset of bs x k per distribution keeps the run short)
+def test_reference_benchmark_distributions(ff, oracle, dist, has_rs):
+    # every distribution of benchmark/bench_topk.py:60-96 on four points of its grid
     from flash_float_jit_kernels_b200 import workloads as W
     for bs, k, seq in [(1, 2048, 16384), (2, 512, 65536), (4, 1024, 98304), (8, 2048, 120000)]:
         s, l, rs = W.reference_style(bs, seq, has_rs, dist, seed=42)
         run_case(ff, oracle, s, l, k, rs)
+
+
+@pytest.mark.parametrize("has_rs", [False, True])
+@pytest.mark.parametrize("bs", [1, 2, 4, 8])
+def test_reference_benchmark_whole_grid(ff, oracle, bs, has_rs):
+    # the whole (bs, k, seq_len, has_row_starts) grid of benchmark/bench_topk.py:418-431 on the
+    # distribution that benchmark runs ("gaussian", bench_topk.py:437)
+    from flash_float_jit_kernels_b200 import workloads as W
+    assert bs in W.REFERENCE_GRID_BS
+    for seq in W.REFERENCE_GRID_SEQ_LEN:
+        s, l, rs = W.reference_style(bs, seq, has_rs, "gaussian", seed=42 + seq)
+        sd = s.cuda()
+        for k in W.REFERENCE_GRID_K:
+            run_case(ff, oracle, s, l, k, rs, score_dev=sd)
 
 
 @pytest.mark.parametrize("cluster", CLUSTERS)

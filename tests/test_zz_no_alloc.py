@@ -23,7 +23,12 @@ def _call(lib, fn_name, s, lengths, out, k, ws=None):
                               0 if ws is None else ws.numel(), None, stream)
 
 
-def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
+def _free_bytes():
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
+def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row(oracle):
     from flash_float_jit_kernels_b200 import _lib
     assert torch.cuda.is_available()
     lib = _lib.load()
@@ -42,11 +47,14 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
         ref = torch.full((B, k), -7, dtype=torch.int32, device=dev)
         got = torch.full((B, k), -9, dtype=torch.int32, device=dev)
         assert _call(lib, "workspace", s, lengths, ref, k, ws) == 0
+        free_before = _free_bytes()
         assert _call(lib, "static", s, lengths, got, k) == 0, lib.ff_last_error_string()
-        torch.cuda.synchronize()
+        # the driver reports free device memory for the whole GPU: had the call allocated anything
+        # (cudaMalloc rounds up to at least 2 MiB here), the figure would have dropped
+        assert _free_bytes() == free_before, f"call {call}: free device memory changed across the call"
         assert torch.equal(got, ref), f"call {call}: entry points disagree"   # integer indices: exact
-        v = s[0, got[0].long()]
-        assert bool((v[:-1] >= v[1:]).all())
+        exp = oracle.topk_c(s.cpu().numpy(), lengths.cpu().numpy(), k)         # and both agree with the CPU oracle
+        assert np.array_equal(got.cpu().numpy(), exp), f"call {call}: disagrees with the oracle"
     # short rows take the scratch-free kernel path; the entry point must still agree
     s = torch.randn((3, 5000), generator=g, device=dev)
     l3 = torch.tensor([5000, 17, 4000], dtype=torch.int32, device=dev)
@@ -56,6 +64,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
     assert _call(lib, "static", s, l3, got, 64) == 0
     torch.cuda.synchronize()
     assert torch.equal(got, ref)
+    assert np.array_equal(got.cpu().numpy(), oracle.topk_c(s.cpu().numpy(), l3.cpu().numpy(), 64))
 
 
 def test_static_scratch_entry_rejects_more_rows_than_its_scratch_holds():
