@@ -29,6 +29,11 @@ SIGNATURES = {
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32,
          c_void_p, c_size_t, c_void_p, c_void_p],
     ),
+    "ff_topk_launch_typed": (
+        c_int,
+        [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_int32,
+         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
     "ff_topk_launch_static": (
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32, c_void_p, c_void_p],
@@ -75,6 +80,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
          c_size_t, c_void_p, c_void_p],
     ),
+    "ff_topk_cp_step_emulated_ranks": (
+        c_int,
+        [c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+         c_size_t, c_void_p, c_void_p],
+    ),
     "ff_topk_cp_merge": (
         c_int,
         [c_void_p, c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int32, c_int32,
@@ -86,8 +96,11 @@ FF_EPILOGUE_INDEX = 0
 FF_EPILOGUE_PAGE_TABLE = 1
 FF_EPILOGUE_ADD_OFFSET = 2
 FF_TOPK_MAX_K = 2048
+FF_DTYPE_F32, FF_DTYPE_BF16, FF_DTYPE_F16 = 0, 1, 2
 FF_STATUS_WAIT_TIMEOUT = 2
 FF_STATUS_HINT_MISSED = 8
+FF_STATUS_CP_SECOND_ROUND = 16
+TRACE_SLOTS = 40
 
 
 class LibraryMissingError(RuntimeError):

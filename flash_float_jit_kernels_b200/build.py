@@ -87,6 +87,37 @@ def build_indexer_library(force: bool = False, verbose: bool = False, extra_flag
     return _compile(out, INDEXER_SOURCES, verbose, extra_flags)
 
 
+TVMFFI_LIB_NAME = "libff_topk_tvmffi.so"   # the reference's own FFI symbol, forwarding to libff_topk.so
+
+
+def tvmffi_lib_path() -> Path:
+    return CSRC / TVMFFI_LIB_NAME
+
+
+def build_tvmffi_module(force: bool = False) -> Path:
+    """Compile ``csrc/ff_topk_tvm_ffi.cc`` (host code, g++) into ``csrc/libff_topk_tvmffi.so``: a
+    TVM-FFI module exporting ``fast_topk`` as the reference's wrapper calls it
+    (``jit_kernel/topk_indexer.py:141-149``).  Needs the ``tvm_ffi`` package (headers and library)."""
+    import tvm_ffi.libinfo as li
+    out = tvmffi_lib_path()
+    src = CSRC / "ff_topk_tvm_ffi.cc"
+    deps = [src, INCLUDE / "ff_topk.h"]
+    if not force and out.exists() and all(d.stat().st_mtime <= out.stat().st_mtime for d in deps):
+        return out
+    build_library()
+    tvm_lib = Path(li.find_libtvm_ffi())
+    cxx = shutil.which("g++") or "g++"
+    cmd = [cxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-o", str(out), str(src),
+           f"-I{li.find_include_path()}", f"-I{li.find_dlpack_include_path()}",
+           f"-L{CSRC}", "-l:" + LIB_NAME, f"-L{tvm_lib.parent}", "-ltvm_ffi",
+           "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tvm_lib.parent}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + res.stdout + res.stderr)
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
     print(build_indexer_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_tvmffi_module(force="--force" in sys.argv))

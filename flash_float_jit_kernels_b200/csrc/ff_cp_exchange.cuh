@@ -91,15 +91,15 @@ struct RunSource {
   }
 };
 
-// Waits for the value entries of all world x k candidates of the row and stages their
-// monotone keys in run_keys[world][k] (shared memory).  Sixteen entries per thread are in
-// flight at a time (with 8 ranks a thread of a 512-thread CTA stages 32 entries, and every
-// round of loads costs a trip to L2 or memory).  Returns false (uniformly) if an entry did
-// not arrive in time.
-__device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, int k, uint32_t step,
+// Waits for the value entries of the first S candidates of every rank's run of the row and stages
+// their monotone keys in run_keys[world][S] (shared memory).  Sixteen entries per thread are in
+// flight at a time (every round of loads costs a trip to L2 or memory).  Returns false
+// (uniformly) if an entry did not arrive in time.
+__device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, int k, int S, uint32_t step,
                                                uint32_t* run_keys) {
   constexpr int kInFlight = 16;
-  const int n_cand = world * k;
+  (void)k;
+  const int n_cand = world * S;
   const int nthreads = static_cast<int>(blockDim.x);
   const unsigned long long t0 = global_ns();
   bool ok = true;
@@ -109,8 +109,8 @@ __device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, 
     for (int u = 0; u < kInFlight; ++u) {
       const int i = i0 + u * nthreads;
       if (i < n_cand) {
-        const int q = i / k;
-        e[u] = ld_entry(src.value_entry(q, i - q * k));
+        const int q = i / S;
+        e[u] = ld_entry(src.value_entry(q, i - q * S));
       }
     }
 #pragma unroll
@@ -119,8 +119,8 @@ __device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, 
       if (i < n_cand) {
         uint32_t bits = e[u].x;
         if (e[u].y != step) {   // not there yet: poll (rare once the peers are in step)
-          const int q = i / k;
-          bits = await_entry(src.value_entry(q, i - q * k), e[u], step, t0, ok);
+          const int q = i / S;
+          bits = await_entry(src.value_entry(q, i - q * S), e[u], step, t0, ok);
         }
         run_keys[i] = run_key_of_bits(bits);
       }
@@ -129,18 +129,18 @@ __device__ __forceinline__ bool stage_run_keys(const RunSource& src, int world, 
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-// Global rank of candidate j (key `key`) of run `run` among `world` runs of k keys each, all
+// Global rank of candidate j (key `key`) of run `run` among `world` runs of S keys each, all
 // in shared memory in descending order with key 0 in unused tail positions.  Every rank's run
 // is in canonical order (value desc, index asc) and the shards are contiguous in rank order, so
 //   rank = j + sum over q < run of #(key_q >= key) + sum over q > run of #(key_q > key),
 // each term one binary search.
-__device__ __forceinline__ int rank_among_runs(const uint32_t* run_keys, int world, int k, int run, int j,
+__device__ __forceinline__ int rank_among_runs(const uint32_t* run_keys, int world, int S, int run, int j,
                                                uint32_t key) {
   int rank = j;
   for (int q = 0; q < world; ++q) {
     if (q == run) continue;
-    const uint32_t* keys = run_keys + q * k;
-    int lo = 0, hi = k;
+    const uint32_t* keys = run_keys + q * S;
+    int lo = 0, hi = S;
     while (lo < hi) {
       const int mid = (lo + hi) >> 1;
       const uint32_t kq = keys[mid];
@@ -152,23 +152,39 @@ __device__ __forceinline__ int rank_among_runs(const uint32_t* run_keys, int wor
   return rank;
 }
 
-// Ranks candidates [begin, end) of the row's world x k and writes each winner's global
+// Whether the first k of the merged prefixes (run_keys[world][S], S < k) are the first k of the
+// merged full runs: true exactly when no run's LAST prefix candidate ranks among the first k
+// (everything behind it in its run is below it, so it cannot rank there either).  An unused
+// last position (key 0) means that run was sent whole.  One thread per run checks; the answer
+// is uniform over the CTA (and over every CTA and rank that stages the same keys).
+__device__ __forceinline__ bool prefixes_suffice(const uint32_t* run_keys, int world, int S, int k) {
+  bool short_of = false;
+  if (static_cast<int>(threadIdx.x) < world) {
+    const int q = threadIdx.x;
+    const uint32_t key = run_keys[q * S + S - 1];
+    short_of = key != 0u && rank_among_runs(run_keys, world, S, q, S - 1, key) < k;
+  }
+  return __syncthreads_or(short_of ? 1 : 0) == 0;
+}
+
+// Ranks candidates [begin, end) of the row's world x S staged ones and writes each winner's global
 // index straight to its output position.  run_keys must be staged.  Returns false if an index
 // entry did not arrive in time (thread-local).
-__device__ __forceinline__ bool rank_and_write(const RunSource& src, const uint32_t* run_keys, int world, int k,
+__device__ __forceinline__ bool rank_and_write(const RunSource& src, const uint32_t* run_keys, int world, int k, int S,
                                                uint32_t step, int begin, int end, int32_t* out_row) {
   const unsigned long long t0 = global_ns();
   bool ok = true;
   for (int c = begin + threadIdx.x; c < end; c += blockDim.x) {
     const uint32_t key = run_keys[c];
     if (key == 0u) continue;   // no candidate here
-    const int run = c / k;
-    const int j = c - run * k;
+    const int run = c / S;
+    const int j = c - run * S;
     const uint32_t* ie = src.index_entry(run, j);
     const uint2 first = ld_entry(ie);
-    const int rank = rank_among_runs(run_keys, world, k, run, j, key);
+    const int rank = rank_among_runs(run_keys, world, S, run, j, key);
+    if (rank >= k) continue;   // (its index entry need not be waited for)
     const uint32_t gidx = await_entry(ie, first, step, t0, ok);
-    if (rank < k && ok) out_row[rank] = static_cast<int32_t>(gidx);
+    if (ok) out_row[rank] = static_cast<int32_t>(gidx);
   }
   return ok;
 }
@@ -203,10 +219,10 @@ __global__ void __launch_bounds__(1024) cp_merge_sorted_kernel(const CpMergePara
   src.base = p.recv_even + static_cast<int64_t>(step & 1u) * p.parity_words;
   src.slot_words = p.slot_words;
   src.row_words = 4 * static_cast<int64_t>(row) * k;
-  bool ok = stage_run_keys(src, p.world, k, step, run_keys);
+  bool ok = stage_run_keys(src, p.world, k, k, step, run_keys);   // the send launch delivered whole runs
   const int begin = blockIdx.x * blockDim.x;
   const int end = min(p.world * k, begin + static_cast<int>(blockDim.x));
-  ok = rank_and_write(src, run_keys, p.world, k, step, begin, end, p.out_idx + static_cast<int64_t>(row) * k) && ok;
+  ok = rank_and_write(src, run_keys, p.world, k, k, step, begin, end, p.out_idx + static_cast<int64_t>(row) * k) && ok;
   if (!ok && p.status != nullptr) atomicOr(p.status, 2);
 }
 

@@ -95,6 +95,10 @@ void init_device(int device) {
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePush>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePushHinted>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true, ff::kModePlain>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePlain, __nv_bfloat16>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted, __nv_bfloat16>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePlain, __half>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted, __half>);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(ff::cp_merge_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              ff::kMaxPeers * ff::kMaxK * static_cast<int>(sizeof(uint32_t)));
@@ -188,7 +192,7 @@ int choose_groups(int device, int32_t B, int64_t L_width, size_t workspace_bytes
 }
 
 template <bool HAS_MAP>
-int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
+int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream, int dtype = FF_DTYPE_F32) {
   cudaLaunchConfig_t cfg = {};
   const int groups = p.groups > 1 ? p.groups : 1;
   cfg.gridDim = dim3(static_cast<unsigned>(p.B) * cluster * groups, 1, 1);
@@ -209,11 +213,19 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream) {
   cfg.numAttrs = (groups > 1 || p.push_fused != 0) ? 2 : 1;
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
+  q.block_base = 0;
+  q.grid_ctas = static_cast<int32_t>(cfg.gridDim.x);
 
   // one instantiation per mode: the plain select carries no code of the others
   cudaError_t e;
   const bool hints = q.hint_in != nullptr || q.hint_out != nullptr;
-  if (!HAS_MAP && q.push_world > 0 && hints)
+  if (!HAS_MAP && dtype == FF_DTYPE_BF16)
+    e = hints ? cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted, __nv_bfloat16>, q)
+              : cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePlain, __nv_bfloat16>, q);
+  else if (!HAS_MAP && dtype == FF_DTYPE_F16)
+    e = hints ? cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted, __half>, q)
+              : cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePlain, __half>, q);
+  else if (!HAS_MAP && q.push_world > 0 && hints)
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePushHinted>, q);
   else if (!HAS_MAP && q.push_world > 0)
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePush>, q);
@@ -334,8 +346,8 @@ int ff_topk_set_groups_override(int32_t g) {
 
 namespace {
 
-int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t* lengths,
-                          const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
+int transform_launch_impl(const void* scores_any, int dtype, int64_t row_stride, const int32_t* lengths,
+                          const int32_t* row_starts, void* out_any, int index_bits, int32_t B, int64_t L_width,
                           int32_t k, int32_t epilogue, const int32_t* table,
                           int64_t table_stride, const int32_t* cu_seqlens_q,
                           int32_t n_table_rows, const int32_t* offsets, const float* hint_in,
@@ -344,11 +356,15 @@ int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t
   int rc = check_common(B, L_width, k);
   if (rc != 0) return rc;
   if (B == 0) return 0;
-  if (scores == nullptr || lengths == nullptr || out == nullptr)
+  const float* scores = static_cast<const float*>(scores_any);
+  if (scores == nullptr || lengths == nullptr || out_any == nullptr)
     return fail(FF_ERR_NULL, "scores, lengths and out must not be NULL");
   if (row_stride < 0) return fail(FF_ERR_BAD_SHAPE, "negative row_stride");
-  if ((reinterpret_cast<uintptr_t>(scores) & 3u) != 0)
-    return fail(FF_ERR_BAD_SHAPE, "scores must be 4-byte aligned");
+  if (dtype != FF_DTYPE_F32 && dtype != FF_DTYPE_BF16 && dtype != FF_DTYPE_F16)
+    return fail(FF_ERR_BAD_SHAPE, "score_dtype must be FF_DTYPE_F32, FF_DTYPE_BF16 or FF_DTYPE_F16");
+  if (index_bits != 32 && index_bits != 64) return fail(FF_ERR_BAD_SHAPE, "index_bits must be 32 or 64");
+  if ((reinterpret_cast<uintptr_t>(scores) & (dtype == FF_DTYPE_F32 ? 3u : 1u)) != 0)
+    return fail(FF_ERR_BAD_SHAPE, "scores must be aligned to their element size");
   if (epilogue == FF_EPILOGUE_PAGE_TABLE) {
     if (table == nullptr) return fail(FF_ERR_NULL, "page-table epilogue needs a table");
     if (cu_seqlens_q != nullptr && n_table_rows < 1)
@@ -366,7 +382,8 @@ int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t
   p.row_stride = row_stride;
   p.lengths = lengths;
   p.row_starts = row_starts;
-  p.out_idx = out;
+  if (index_bits == 64) p.out_idx64 = static_cast<int64_t*>(out_any);
+  else p.out_idx = static_cast<int32_t*>(out_any);
   p.B = B;
   p.k = k;
   p.L_width = L_width;
@@ -385,12 +402,21 @@ int transform_launch_impl(const float* scores, int64_t row_stride, const int32_t
     p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster, hint_in != nullptr);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
-  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream), dtype);
 }
 
 }  // namespace
 
 extern "C" {
+
+int ff_topk_launch_typed(const void* scores, int32_t score_dtype, int64_t row_stride, const int32_t* lengths,
+                         const int32_t* row_starts, void* out_idx, int32_t index_bits, int32_t B, int64_t L_width,
+                         int32_t k, const float* hint_in, float* hint_out, void* workspace, size_t workspace_bytes,
+                         int32_t* status, void* stream) {
+  return transform_launch_impl(scores, score_dtype, row_stride, lengths, row_starts, out_idx, index_bits, B, L_width,
+                               k, FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, hint_in, hint_out, workspace,
+                               workspace_bytes, status, stream);
+}
 
 int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int32_t* lengths,
                              const int32_t* row_starts, int32_t* out, int32_t B, int64_t L_width,
@@ -398,8 +424,8 @@ int ff_topk_transform_launch(const float* scores, int64_t row_stride, const int3
                              int64_t table_stride, const int32_t* cu_seqlens_q,
                              int32_t n_table_rows, const int32_t* offsets, void* workspace,
                              size_t workspace_bytes, int32_t* status, void* stream) {
-  return transform_launch_impl(scores, row_stride, lengths, row_starts, out, B, L_width, k, epilogue, table,
-                               table_stride, cu_seqlens_q, n_table_rows, offsets, nullptr, nullptr, workspace,
+  return transform_launch_impl(scores, FF_DTYPE_F32, row_stride, lengths, row_starts, out, 32, B, L_width, k, epilogue,
+                               table, table_stride, cu_seqlens_q, n_table_rows, offsets, nullptr, nullptr, workspace,
                                workspace_bytes, status, stream);
 }
 
@@ -407,7 +433,7 @@ int ff_topk_launch_hinted(const float* scores, int64_t row_stride, const int32_t
                           const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
                           int32_t k, const float* hint_in, float* hint_out, void* workspace,
                           size_t workspace_bytes, int32_t* status, void* stream) {
-  return transform_launch_impl(scores, row_stride, lengths, row_starts, out_idx, B, L_width, k,
+  return transform_launch_impl(scores, FF_DTYPE_F32, row_stride, lengths, row_starts, out_idx, 32, B, L_width, k,
                                FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, hint_in, hint_out, workspace,
                                workspace_bytes, status, stream);
 }
@@ -647,6 +673,28 @@ int cp_fused_setting() {
   return env != nullptr ? atoi(env) : -1;
 }
 
+// How many of a rank's k candidates per row go to the peers right away in a single-kernel step.
+// Each of `world` contiguous shards holds about k / world of the row's top-k; twice that (and never
+// fewer than 256) is sent, so that on rows whose winners are spread over the shards the first round
+// is enough, and the link carries 2 k entries per rank instead of world * k.  Rows whose winners
+// crowd into few shards take the second round (exact either way).  FF_TOPK_CP_PREFIX overrides.
+int cp_prefix(int world, int k) {
+  const char* env = getenv("FF_TOPK_CP_PREFIX");
+  int s = env != nullptr ? atoi(env) : 0;
+  if (s <= 0) {
+    if (world <= 2) return k;
+    s = (2 * k + world - 1) / world;
+    if (s < 256) s = 256;
+  }
+  return s < k ? (s < 1 ? 1 : s) : k;
+}
+
+// The parameter block of one rank's context-parallel send launch (shared by the real entry points
+// and the several-ranks-in-one-launch test entry).  Returns 0 and the cluster size.
+int cp_fill_params(FfCpExchange* ex, const float* scores, int64_t row_stride, const int32_t* lengths,
+                   int64_t L_width, int64_t shard_offset, const float* hint_in, float* hint_out, void* workspace,
+                   size_t workspace_bytes, int32_t* status, int device, ff::TopkParams* out, int* cluster_out);
+
 // fused_out == nullptr: send only (the merge is a later launch).  Otherwise the launch
 // merges too, if all its CTAs fit on the device together; *did_fuse tells.
 int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,
@@ -656,18 +704,40 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
   if (did_fuse != nullptr) *did_fuse = false;
   if (handle == nullptr) return fail(FF_ERR_NULL, "exchange handle must not be NULL");
   FfCpExchange* ex = static_cast<FfCpExchange*>(handle);
+  int device = 0;
+  int rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  ff::TopkParams p = {};
+  int cluster = 1;
+  rc = cp_fill_params(ex, scores, row_stride, lengths, L_width, shard_offset, hint_in, hint_out, workspace,
+                      workspace_bytes, status, device, &p, &cluster);
+  if (rc != 0) return rc;
+  if (fused_out != nullptr && cp_fused_setting() != 0) {
+    int log2c = 0;
+    while ((1 << log2c) < cluster) ++log2c;
+    const int64_t clusters = static_cast<int64_t>(ex->B) * (p.groups > 1 ? p.groups : 1);
+    if (log2c < 5 && clusters <= g_active_clusters[device][log2c]) {
+      p.push_fused = 1;
+      p.push_prefix = cp_prefix(ex->world, ex->k);   // only a launch that merges itself can ask for the rest
+      p.out_idx = fused_out;
+      if (did_fuse != nullptr) *did_fuse = true;
+    }
+  }
+  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
+}
+
+int cp_fill_params(FfCpExchange* ex, const float* scores, int64_t row_stride, const int32_t* lengths,
+                   int64_t L_width, int64_t shard_offset, const float* hint_in, float* hint_out, void* workspace,
+                   size_t workspace_bytes, int32_t* status, int device, ff::TopkParams* out, int* cluster_out) {
   for (int p = 0; p < ex->world; ++p)
     if (ex->peer[p] == nullptr) return fail(FF_ERR_NULL, "exchange: a peer is not mapped yet");
-  // One launch: the shard-local select writes its k candidates per row straight into every
-  // peer's receive slot as self-validating entries (no separate push kernel, no flags).
+  // One launch: the shard-local select writes its candidates straight into the peers' receive
+  // slots as self-validating entries (no separate push kernel, no flags).
   int rc = check_common(ex->B, L_width, ex->k);
   if (rc != 0) return rc;
   if (scores == nullptr || lengths == nullptr) return fail(FF_ERR_NULL, "scores and lengths must not be NULL");
   if (shard_offset < 0 || shard_offset + L_width > 0x7fffffffLL)
     return fail(FF_ERR_TOO_LARGE, "shard_offset + L_width exceeds int32 indices");
-  int device = 0;
-  rc = ensure_init(&device);
-  if (rc != 0) return rc;
   ff::TopkParams p = {};
   p.scores = scores;
   p.row_stride = row_stride;
@@ -686,6 +756,7 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
   p.push_rank = ex->rank;
   p.push_slot_words = static_cast<int64_t>(ex->slot_words);
   p.push_ctrl_offset = static_cast<int64_t>(ex->ctrl_offset);
+  p.push_prefix = ex->k;   // a send whose merge is another launch delivers whole runs
   p.hint_in = hint_in;     // guesses of the shard-local threshold, as in ff_topk_launch_hinted
   p.hint_out = hint_out;
   int cluster = choose_cluster(device, ex->B, L_width, ex->k);
@@ -693,17 +764,9 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
     p.groups = choose_groups(device, ex->B, L_width, workspace_bytes, &cluster, hint_in != nullptr);
     p.workspace = static_cast<uint32_t*>(workspace);
   }
-  if (fused_out != nullptr && cp_fused_setting() != 0) {
-    int log2c = 0;
-    while ((1 << log2c) < cluster) ++log2c;
-    const int64_t clusters = static_cast<int64_t>(ex->B) * (p.groups > 1 ? p.groups : 1);
-    if (log2c < 5 && clusters <= g_active_clusters[device][log2c]) {
-      p.push_fused = 1;
-      p.out_idx = fused_out;
-      if (did_fuse != nullptr) *did_fuse = true;
-    }
-  }
-  return launch<false>(p, cluster, static_cast<cudaStream_t>(stream));
+  *out = p;
+  *cluster_out = cluster;
+  return 0;
 }
 
 }  // namespace
@@ -754,6 +817,74 @@ int ff_topk_cp_step(void* handle, const float* scores, int64_t row_stride, const
                     size_t workspace_bytes, int32_t* status, void* stream) {
   return ff_topk_cp_step_hinted(handle, scores, row_stride, lengths, out_idx, L_width, shard_offset, nullptr,
                                 nullptr, workspace, workspace_bytes, status, stream);
+}
+
+int ff_topk_cp_step_emulated_ranks(int32_t n_ranks, void* const* handles, const float* const* scores,
+                                   int64_t row_stride, const int32_t* lengths, int32_t* const* out_idx,
+                                   const int64_t* L_width, const int64_t* shard_offset, float* const* hints,
+                                   void* const* workspaces, size_t workspace_bytes, int32_t* status, void* stream) {
+  if (n_ranks < 1 || n_ranks > ff::kMaxEmulatedRanks) return fail(FF_ERR_BAD_SHAPE, "n_ranks must be in [1, 8]");
+  if (handles == nullptr || scores == nullptr || out_idx == nullptr || L_width == nullptr || shard_offset == nullptr)
+    return fail(FF_ERR_NULL, "NULL argument");
+  int device = 0;
+  int rc = ensure_init(&device);
+  if (rc != 0) return rc;
+  static std::once_flag once;
+  static cudaError_t prep = cudaSuccess;
+  std::call_once(once, [] { prep = prepare_kernel(ff::topk_emulated_ranks_kernel<ff::kModePushHinted>); });
+  if (prep != cudaSuccess) return fail_cuda(prep, "cudaFuncSetAttribute(topk_emulated_ranks_kernel)");
+  ff::EmulatedRanks e = {};
+  int cluster = 0, groups = 0;
+  for (int r = 0; r < n_ranks; ++r) {
+    FfCpExchange* ex = static_cast<FfCpExchange*>(handles[r]);
+    if (ex == nullptr || ex->world != n_ranks || ex->rank != r) return fail(FF_ERR_BAD_SHAPE, "handles[r] must be rank r of n_ranks");
+    int c = 1;
+    float* hint = hints != nullptr ? hints[r] : nullptr;
+    void* ws = workspaces != nullptr ? workspaces[r] : nullptr;
+    rc = cp_fill_params(ex, scores[r], row_stride, lengths, L_width[r], shard_offset[r], hint, hint, ws,
+                        ws != nullptr ? workspace_bytes : 0, status, device, &e.rank[r], &c);
+    if (rc != 0) return rc;
+    const int g = e.rank[r].groups > 1 ? e.rank[r].groups : 1;
+    if (r == 0) {
+      cluster = c;
+      groups = g;
+    } else if (c != cluster || g != groups) {
+      return fail(FF_ERR_BAD_SHAPE, "emulated ranks need shards of one launch shape (force it with the overrides)");
+    }
+    e.rank[r].push_fused = 1;
+    e.rank[r].push_prefix = cp_prefix(n_ranks, ex->k);
+    e.rank[r].out_idx = out_idx[r];
+    e.rank[r].trace = g_trace.load(std::memory_order_relaxed);
+  }
+  const int B = e.rank[0].B;
+  const int per_rank = B * cluster * groups;
+  int log2c = 0;
+  while ((1 << log2c) < cluster) ++log2c;
+  if (static_cast<int64_t>(n_ranks) * B * groups > g_active_clusters[device][log2c])
+    return fail(FF_ERR_TOO_LARGE, "emulated ranks: the CTAs of all ranks must be resident at once");
+  for (int r = 0; r < n_ranks; ++r) {
+    e.rank[r].block_base = r * per_rank;
+    e.rank[r].grid_ctas = per_rank;
+  }
+  e.ctas_per_rank = per_rank;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(n_ranks * per_rank), 1, 1);
+  cfg.blockDim = dim3(ff::kThreads, 1, 1);
+  cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeCooperative;   // the ranks' CTAs wait for one another
+  attr[1].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, ff::topk_emulated_ranks_kernel<ff::kModePushHinted>, e);
+  if (err != cudaSuccess) return fail_cuda(err, "cudaLaunchKernelEx(topk_emulated_ranks_kernel)");
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return 0;
 }
 
 int ff_topk_cp_step_hinted(void* handle, const float* scores, int64_t row_stride, const int32_t* lengths,

@@ -3,6 +3,8 @@
 // the kernel parameter block.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -55,13 +57,44 @@ __device__ __forceinline__ int32_t comp_index(uint64_t c) {
 }
 __device__ __forceinline__ uint32_t comp_key(uint64_t c) { return static_cast<uint32_t>(c >> 32); }
 
+// Score element types.  A row is always cut into 16-byte units (4 fp32 or 8 sixteen-bit scores);
+// a 16-bit score is widened to fp32 exactly, so keys, threshold compares and results are those of
+// the fp32 row holding the same values (the reference is fp32 only and leaves a half-precision
+// value type commented out, topk_indexer_radix.cu:563-564).
+template <typename T>
+struct Elem;
+template <>
+struct Elem<float> {
+  static constexpr int kPerUnit = 4;
+  static constexpr int kLog2Bytes = 2;
+  static __device__ __forceinline__ float to_float(float x) { return x; }
+  static __device__ __forceinline__ float from_bits16(uint32_t) { return 0.f; }
+};
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int kPerUnit = 8;
+  static constexpr int kLog2Bytes = 1;
+  static __device__ __forceinline__ float from_bits16(uint32_t b) { return __uint_as_float(b << 16); }
+  static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return from_bits16(__bfloat16_as_ushort(x)); }
+};
+template <>
+struct Elem<__half> {
+  static constexpr int kPerUnit = 8;
+  static constexpr int kLog2Bytes = 1;
+  static __device__ __forceinline__ float from_bits16(uint32_t b) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(b)));
+  }
+  static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+};
+
 constexpr int kMaxPeers = 16;
 struct PeerPtrs {
   uint32_t* base[kMaxPeers];   // each rank's exchange allocation as mapped in this process
 };
 
 struct TopkParams {
-  const float* scores;         // [B, row_stride]
+  const float* scores;         // [B, row_stride]; bf16 / fp16 rows are passed through this pointer too (the
+                               // kernel instantiation knows the element type); row_stride counts elements
   int64_t row_stride;
   const int32_t* lengths;      // [B] (global lengths in context-parallel mode)
   const int32_t* row_starts;   // [B] or null
@@ -69,6 +102,7 @@ struct TopkParams {
   int32_t seg_len;             // merge mode: position i lives at (i / seg_len) * seg_stride + i % seg_len
   int64_t seg_stride;
   int32_t* out_idx;            // [B, k]
+  int64_t* out_idx64;          // [B, k] 64-bit indices instead of out_idx when non-null
   float* out_val;              // [B, k] or null
   int32_t B;
   int32_t k;
@@ -92,10 +126,14 @@ struct TopkParams {
   int64_t push_slot_words;
   int64_t push_ctrl_offset;    // words from an exchange buffer's start to its control words
   int32_t push_fused;          // 1: the same launch also waits for the peers and merges (single-kernel step)
+  int32_t push_prefix;         // candidates per row sent to the peers right away (the first push_prefix of the k);
+                               // the rest stay in this rank's own slot until a merge finds that it needs them
+  int32_t block_base;          // first CTA of this rank's part of the grid (0 except when several ranks are
+  int32_t grid_ctas;           // played by ONE launch on one GPU), and the number of CTAs of that part
   unsigned long long* trace;   // optional stage stamps, [grid CTAs][kTraceSlots] (debug aid)
 };
 
-constexpr int kTraceSlots = 32;
+constexpr int kTraceSlots = 40;
 
 // Stage stamp for the per-CTA timeline: SM cycle counter, thread 0 only.
 #define FF_TRACE(p, slot)                                                                 \

@@ -111,10 +111,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Geometry of one row as seen by one CTA of the cluster.  The row is cut into
-// 16-byte units on absolute addresses so interior units load as float4 even
+// 16-byte units on absolute addresses so interior units load whole even
 // when row_starts or an odd row stride misaligns the window.
+template <typename T>
 struct Chunk {
-  const float* abase;     // 16-byte aligned, abase + mis == first element of the window
+  const T* abase;         // 16-byte aligned, abase + mis == first element of the window
   const int32_t* imap;    // merge mode: index plane, addressed like the value plane
   int seg_len;            // merge mode: position i -> (i / seg_len) * seg_stride + i % seg_len
   int64_t seg_stride;
@@ -131,10 +132,12 @@ __device__ __forceinline__ int64_t seg_addr(int i, int seg_len, int64_t seg_stri
   return static_cast<int64_t>(seg) * seg_stride + (i - seg * seg_len);
 }
 
-__device__ __forceinline__ Chunk make_chunk(const float* row, const int32_t* imap, int len, int C,
-                                            int rank, int seg_len, int64_t seg_stride) {
-  Chunk c;
-  c.mis = static_cast<int>((reinterpret_cast<uintptr_t>(row) >> 2) & 3);
+template <typename T>
+__device__ __forceinline__ Chunk<T> make_chunk(const T* row, const int32_t* imap, int len, int C,
+                                               int rank, int seg_len, int64_t seg_stride) {
+  constexpr int kPU = Elem<T>::kPerUnit;
+  Chunk<T> c;
+  c.mis = static_cast<int>((reinterpret_cast<uintptr_t>(row) >> Elem<T>::kLog2Bytes) & (kPU - 1));
   c.abase = row - c.mis;
   c.imap = imap;
   c.len = len;
@@ -145,9 +148,9 @@ __device__ __forceinline__ Chunk make_chunk(const float* row, const int32_t* ima
     c.pb = min(len, rank * pper);
     c.pe = min(len, c.pb + pper);
   }
-  const int U = static_cast<int>((static_cast<int64_t>(len) + c.mis + 3) >> 2);
+  const int U = static_cast<int>((static_cast<int64_t>(len) + c.mis + (kPU - 1)) / kPU);
   const bool head_partial = c.mis != 0;
-  const bool tail_partial = ((len + c.mis) & 3) != 0;
+  const bool tail_partial = ((len + c.mis) & (kPU - 1)) != 0;
   const int full_begin = head_partial ? 1 : 0;
   const int full_end = tail_partial ? U - 1 : U;
   const int per = (U + C - 1) / C;
@@ -164,18 +167,38 @@ __device__ __forceinline__ Chunk make_chunk(const float* row, const int32_t* ima
 
 // The (at most one) element of a partial first / last unit this thread owns:
 // returns its window position or -1, value in x.  Scalar load of a valid lane only.
-__device__ __forceinline__ int partial_element(const Chunk& c, float& x) {
+template <typename T>
+__device__ __forceinline__ int partial_element(const Chunk<T>& c, float& x) {
+  constexpr int kPU = Elem<T>::kPerUnit;
   int pos = -1;
-  if (threadIdx.x < 4 && c.head) {
+  if (threadIdx.x < kPU && c.head) {
     pos = static_cast<int>(threadIdx.x) - c.mis;
-    if (pos >= 0 && pos < c.len) x = c.abase[threadIdx.x]; else pos = -1;
+    if (pos >= 0 && pos < c.len) x = Elem<T>::to_float(c.abase[threadIdx.x]); else pos = -1;
   }
-  if (threadIdx.x >= 32 && threadIdx.x < 36 && c.tail) {
-    const int l4 = static_cast<int>(threadIdx.x) - 32;
-    pos = 4 * c.tail_unit - c.mis + l4;
-    if (pos >= 0 && pos < c.len) x = c.abase[4 * c.tail_unit + l4]; else pos = -1;
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + kPU && c.tail) {
+    const int l = static_cast<int>(threadIdx.x) - 32;
+    pos = kPU * c.tail_unit - c.mis + l;
+    if (pos >= 0 && pos < c.len) x = Elem<T>::to_float(c.abase[kPU * c.tail_unit + l]); else pos = -1;
   }
   return pos;
+}
+
+// One 16-byte unit as floats: v[0 .. kPerUnit).
+template <typename T>
+__device__ __forceinline__ void unpack_unit(const uint4& w, float (&v)[Elem<T>::kPerUnit]) {
+  if constexpr (Elem<T>::kPerUnit == 4) {
+    v[0] = __uint_as_float(w.x);
+    v[1] = __uint_as_float(w.y);
+    v[2] = __uint_as_float(w.z);
+    v[3] = __uint_as_float(w.w);
+  } else {
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = Elem<T>::from_bits16(ws[i] & 0xffffu);
+      v[2 * i + 1] = Elem<T>::from_bits16(ws[i] >> 16);
+    }
+  }
 }
 
 // Generic (cold) sweep with direct global loads: calls f(x, index) for every
@@ -183,25 +206,26 @@ __device__ __forceinline__ int partial_element(const Chunk& c, float& x) {
 // and on the rare paths (deeper digit levels over a chunk that did not fit the
 // candidate buffer).  In merge mode f receives index -1 for ignored entries and
 // pre is not applied.
-template <bool HAS_MAP, typename Pre, typename F>
-__device__ __forceinline__ void for_each_in_chunk(const Chunk& c, Pre&& pre, F&& f) {
-  if (HAS_MAP) {
-    const float* vals = c.abase + c.mis;
+template <bool HAS_MAP, typename T, typename Pre, typename F>
+__device__ __forceinline__ void for_each_in_chunk(const Chunk<T>& c, Pre&& pre, F&& f) {
+  constexpr int kPU = Elem<T>::kPerUnit;
+  if constexpr (HAS_MAP) {
+    const T* vals = c.abase + c.mis;
     for (int i = c.pb + threadIdx.x; i < c.pe; i += kThreads) {
       const int64_t a = seg_addr(i, c.seg_len, c.seg_stride);
-      f(vals[a], c.imap[a]);
+      f(Elem<T>::to_float(vals[a]), c.imap[a]);
     }
     return;
   }
-  const float4* p4 = reinterpret_cast<const float4*>(c.abase);
+  const uint4* p4 = reinterpret_cast<const uint4*>(c.abase);
 #pragma unroll 1
   for (int u = c.fb + threadIdx.x; u < c.fe; u += kThreads) {
-    const float4 v = __ldg(p4 + u);
-    const int pos = 4 * u - c.mis;
-    if (pre(v.x)) f(v.x, pos);
-    if (pre(v.y)) f(v.y, pos + 1);
-    if (pre(v.z)) f(v.z, pos + 2);
-    if (pre(v.w)) f(v.w, pos + 3);
+    float v[kPU];
+    unpack_unit<T>(__ldg(p4 + u), v);
+    const int pos = kPU * u - c.mis;
+#pragma unroll
+    for (int e = 0; e < kPU; ++e)
+      if (pre(v[e])) f(v[e], pos + e);
   }
   float x = 0.f;
   const int pos = partial_element(c, x);
@@ -313,10 +337,63 @@ __device__ __forceinline__ void stream_pass(TileStream& s, F&& process) {
   }
 }
 
-__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
+}
+// One score of a tile in shared memory: element e of unit lu.
+template <typename T>
+__device__ __forceinline__ float lds_score(uint32_t tile, int lu, int e) {
+  if constexpr (Elem<T>::kPerUnit == 4) {
+    float x;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 4u * e));
+    return x;
+  } else {
+    unsigned short b;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(b) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 2u * e));
+    return Elem<T>::from_bits16(b);
+  }
+}
+
+// A thread's hit mask over its units of one tile: one bit per score, 32 or 64 of them.
+template <typename T>
+struct HitMask {
+  using type = uint32_t;
+};
+template <>
+struct HitMask<__nv_bfloat16> {
+  using type = unsigned long long;
+};
+template <>
+struct HitMask<__half> {
+  using type = unsigned long long;
+};
+__device__ __forceinline__ int hit_count(uint32_t m) { return __popc(m); }
+__device__ __forceinline__ int hit_count(unsigned long long m) { return __popcll(m); }
+__device__ __forceinline__ int first_hit(uint32_t m) { return __ffs(m) - 1; }
+__device__ __forceinline__ int first_hit(unsigned long long m) { return __ffsll(static_cast<long long>(m)) - 1; }
+
+// The scores of this thread's units of a tile that are not below vmin, as a bit mask
+// (bit j * kPerUnit + e: element e of unit threadIdx.x + j * kThreads).
+template <typename T>
+__device__ __forceinline__ typename HitMask<T>::type tile_hits(uint32_t tile, int units, float vmin) {
+  constexpr int kPU = Elem<T>::kPerUnit;
+  using Mask = typename HitMask<T>::type;
+  Mask hits = 0;
+#pragma unroll
+  for (int j = 0; j < kTileUnits / kThreads; ++j) {
+    const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
+    if (lu < units) {
+      float v[kPU];
+      unpack_unit<T>(lds_u4(tile + 16u * static_cast<uint32_t>(lu)), v);
+      uint32_t h = 0u;
+#pragma unroll
+      for (int e = 0; e < kPU; ++e) h |= (!(v[e] < vmin) ? 1u : 0u) << e;
+      hits |= static_cast<Mask>(h) << (kPU * j);
+    }
+  }
+  return hits;
 }
 
 // Raw 13-bit digit of a score: sign | exponent | top 4 mantissa bits of x + 0.0f.
@@ -400,49 +477,38 @@ __device__ __noinline__ void classify_value(const LevelCtx* c, float x, int32_t 
 }
 
 // Second sweep over one tile: every value not below vmin is a hit; the hits'
-// composites are appended to list[0, cap).  A warp tests its 32 values per lane
+// composites are appended to list[0, cap).  A warp tests its values (32 or 64 per lane)
 // with float compares and votes once.  Only a warp that saw a hit assigns list
-// slots: the per-lane hit counts (0..32) are prefix-summed with six ballots over
-// their bit planes, one lane does the single shared atomic, and each lane then
+// slots: the per-lane hit counts are prefix-summed with one ballot per bit plane,
+// one lane does the single shared atomic, and each lane then
 // walks its own hit bits, re-reading the value from the tile.
+template <typename T>
 __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
                                              uint64_t* list, int cap, int* counter) {
+  constexpr int kPU = Elem<T>::kPerUnit;
+  constexpr int kPlanes = kPU == 4 ? 6 : 7;   // counts up to 32 or 64
   const int lane = threadIdx.x & 31;
-  uint32_t hits = 0u;
-#pragma unroll
-  for (int j = 0; j < kTileUnits / kThreads; ++j) {
-    const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
-    if (lu < units) {
-      const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
-      const uint32_t h = (!(v.x < vmin) ? 1u : 0u) | (!(v.y < vmin) ? 2u : 0u) |
-                         (!(v.z < vmin) ? 4u : 0u) | (!(v.w < vmin) ? 8u : 0u);
-      hits |= h << (4 * j);
-    }
-  }
-  if (__any_sync(0xffffffffu, hits != 0u)) {
-    const uint32_t n = __popc(hits);
+  auto hits = tile_hits<T>(tile, units, vmin);
+  if (__any_sync(0xffffffffu, hits != 0)) {
+    const uint32_t n = static_cast<uint32_t>(hit_count(hits));
     const uint32_t lt = (1u << lane) - 1u;
-    const uint32_t b0 = __ballot_sync(0xffffffffu, n & 1u);
-    const uint32_t b1 = __ballot_sync(0xffffffffu, n & 2u);
-    const uint32_t b2 = __ballot_sync(0xffffffffu, n & 4u);
-    const uint32_t b3 = __ballot_sync(0xffffffffu, n & 8u);
-    const uint32_t b4 = __ballot_sync(0xffffffffu, n & 16u);
-    const uint32_t b5 = __ballot_sync(0xffffffffu, n & 32u);
-    const int before = __popc(b0 & lt) + 2 * __popc(b1 & lt) + 4 * __popc(b2 & lt) + 8 * __popc(b3 & lt) +
-                       16 * __popc(b4 & lt) + 32 * __popc(b5 & lt);
-    const int total = __popc(b0) + 2 * __popc(b1) + 4 * __popc(b2) + 8 * __popc(b3) + 16 * __popc(b4) +
-                      32 * __popc(b5);
+    int before = 0, total = 0;
+#pragma unroll
+    for (int b = 0; b < kPlanes; ++b) {
+      const uint32_t plane = __ballot_sync(0xffffffffu, n & (1u << b));
+      before += __popc(plane & lt) << b;
+      total += __popc(plane) << b;
+    }
     int base = 0;
     if (lane == 0) base = atomicAdd(counter, total);
     base = __shfl_sync(0xffffffffu, base, 0);
     int pos = base + before;
-    while (hits != 0u) {
-      const int e = __ffs(hits) - 1;
-      hits &= hits - 1u;
-      const int lu = static_cast<int>(threadIdx.x) + (e >> 2) * kThreads;
-      float x;
-      asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 4u * (e & 3)));
-      if (pos < cap) list[pos] = make_comp(key_of(x), 4 * (first_unit + lu) - mis + (e & 3));
+    while (hits != 0) {
+      const int e = first_hit(hits);
+      hits &= hits - 1;
+      const int lu = static_cast<int>(threadIdx.x) + (e / kPU) * kThreads;
+      const float x = lds_score<T>(tile, lu, e & (kPU - 1));
+      if (pos < cap) list[pos] = make_comp(key_of(x), kPU * (first_unit + lu) - mis + (e & (kPU - 1)));
       ++pos;
     }
   }
@@ -451,27 +517,16 @@ __device__ __forceinline__ void collect_tile(uint32_t tile, int units, int first
 // Like collect_tile, but every value not below vmin is handed to on_hit(x, position)
 // instead of being stored: used by the sweeps of the second digit level, where a
 // hit is either counted in the next histogram or stored after an exact test.
-template <typename F>
+template <typename T, typename F>
 __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_unit, int mis, float vmin,
                                           F&& on_hit) {
-  uint32_t hits = 0u;
-#pragma unroll
-  for (int j = 0; j < kTileUnits / kThreads; ++j) {
-    const int lu = static_cast<int>(threadIdx.x) + j * kThreads;
-    if (lu < units) {
-      const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
-      const uint32_t h = (!(v.x < vmin) ? 1u : 0u) | (!(v.y < vmin) ? 2u : 0u) |
-                         (!(v.z < vmin) ? 4u : 0u) | (!(v.w < vmin) ? 8u : 0u);
-      hits |= h << (4 * j);
-    }
-  }
-  while (hits != 0u) {
-    const int e = __ffs(hits) - 1;
-    hits &= hits - 1u;
-    const int lu = static_cast<int>(threadIdx.x) + (e >> 2) * kThreads;
-    float x;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(x) : "r"(tile + 16u * static_cast<uint32_t>(lu) + 4u * (e & 3)));
-    on_hit(x, 4 * (first_unit + lu) - mis + (e & 3));
+  constexpr int kPU = Elem<T>::kPerUnit;
+  auto hits = tile_hits<T>(tile, units, vmin);
+  while (hits != 0) {
+    const int e = first_hit(hits);
+    hits &= hits - 1;
+    const int lu = static_cast<int>(threadIdx.x) + (e / kPU) * kThreads;
+    on_hit(lds_score<T>(tile, lu, e & (kPU - 1)), kPU * (first_unit + lu) - mis + (e & (kPU - 1)));
   }
 }
 
@@ -871,7 +926,13 @@ __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, i
     const uint32_t vbits = idx < 0 ? kNoCandidateBits : bits_of_key(key);
     const uint32_t gidx = idx < 0 ? 0xffffffffu : static_cast<uint32_t>(idx + p.shard_offset);
     const size_t at = push.off + 4 * (static_cast<size_t>(row) * p.k + j);
-    for (int q = 0; q < p.push_world; ++q) st_entry(p.push_peers.base[q] + at, vbits, gidx, push.step);
+    // This rank's own slot gets every candidate; the peers get the first push_prefix of the run
+    // now, and the rest only if a merge finds that the prefixes do not hold the whole top-k.
+    st_entry(p.push_peers.base[p.push_rank] + at, vbits, gidx, push.step);
+    if (j < p.push_prefix) {
+      for (int q = 0; q < p.push_world; ++q)
+        if (q != p.push_rank) st_entry(p.push_peers.base[q] + at, vbits, gidx, push.step);
+    }
     return;
   }
   int32_t o;
@@ -884,7 +945,8 @@ __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, i
   } else {
     o = is_map ? idx : static_cast<int32_t>(idx + p.shard_offset);
   }
-  p.out_idx[static_cast<int64_t>(row) * p.k + j] = o;
+  if (p.out_idx64 != nullptr) p.out_idx64[static_cast<int64_t>(row) * p.k + j] = o;
+  else p.out_idx[static_cast<int64_t>(row) * p.k + j] = o;
   if (p.out_val != nullptr) {
     p.out_val[static_cast<int64_t>(row) * p.k + j] =
         idx < 0 ? __uint_as_float(0xff800000u) : __uint_as_float(bits_of_key(key));
@@ -906,9 +968,11 @@ constexpr int kModeHinted = 1;
 constexpr int kModePush = 2;
 constexpr int kModePushHinted = kModePush | kModeHinted;
 
-template <bool HAS_MAP, int MODE>
+template <bool HAS_MAP, int MODE, typename T>
 __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
                                               const PushCtx& push) {
+  static_assert(!HAS_MAP || Elem<T>::kPerUnit == 4, "merge mode selects among fp32 candidates");
+  constexpr int kPU = Elem<T>::kPerUnit;
   constexpr bool kPush = (MODE & kModePush) != 0;
   constexpr bool kHinted = (MODE & kModeHinted) != 0;
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
@@ -921,8 +985,9 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const int C = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());
   const int G = HAS_MAP ? 1 : max(p.groups, 1);       // clusters per row
-  const int row = static_cast<int>(blockIdx.x) / (C * G);
-  const int group = (static_cast<int>(blockIdx.x) / C) % G;
+  const int bid = static_cast<int>(blockIdx.x) - p.block_base;
+  const int row = bid / (C * G);
+  const int group = (bid / C) % G;
   const int n_share = C * G;                           // CTAs working on this row
   const int my_share = group * C + rank;
   uint32_t* ws = G > 1 ? p.workspace + static_cast<size_t>(row) * kWsRowWords : nullptr;
@@ -942,7 +1007,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (l < 0) l = 0;
     len = static_cast<int>(l);
   }
-  const float* rowp = p.scores + static_cast<int64_t>(row) * p.row_stride + rs;
+  const T* rowp = reinterpret_cast<const T*>(p.scores) + static_cast<int64_t>(row) * p.row_stride + rs;
   const int32_t* imap =
       HAS_MAP ? p.idx_map + static_cast<int64_t>(row) * p.row_stride + rs : nullptr;
 
@@ -965,7 +1030,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (!HAS_MAP && p.out_val != nullptr) {
       // Context-parallel shard shorter than k: every position is a candidate, but the
       // merge expects the run in canonical order, so rank the few elements by counting.
-      for (int j = tid; j < len; j += kThreads) stage[j] = make_comp(key_of(rowp[j]), j);
+      for (int j = tid; j < len; j += kThreads) stage[j] = make_comp(key_of(Elem<T>::to_float(rowp[j])), j);
       __syncthreads();
       for (int j = tid; j < k; j += kThreads) {
         if (j >= len) {
@@ -984,19 +1049,19 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         // no more candidates than k slots: pass them through in position order
         const int64_t a = j < len ? seg_addr(j, p.seg_len, p.seg_stride) : 0;
         const int32_t idx = j < len ? imap[a] : -1;
-        emit<kPush>(p, push, row, j, idx, j < len ? key_of(rowp[a]) : 0u, true, table_row);
+        emit<kPush>(p, push, row, j, idx, j < len ? key_of(Elem<T>::to_float(rowp[a])) : 0u, true, table_row);
       } else {
         const int n = HAS_MAP ? glen : len;
         const bool v = j < n;
         uint32_t key = 0u;
-        if (v && !HAS_MAP && p.out_val != nullptr) key = key_of(rowp[j]);
+        if (v && !HAS_MAP && p.out_val != nullptr) key = key_of(Elem<T>::to_float(rowp[j]));
         emit<kPush>(p, push, row, j, v ? j : -1, key, HAS_MAP, table_row);
       }
     }
     return;
   }
 
-  const Chunk chunk = make_chunk(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
+  const Chunk<T> chunk = make_chunk<T>(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
 
   TileStream ts;
@@ -1097,7 +1162,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   __syncthreads();
   if (kHinted && use_hint) {
     stream_pass(ts, [&](uint32_t tile, int tt, int units) {
-      collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, hint, stage, kSortCap, &sh.stage_count);
+      collect_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, hint, stage, kSortCap, &sh.stage_count);
     });
     {
       float x = 0.f;
@@ -1157,7 +1222,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   for (int i = tid; i < kMaxBins; i += kThreads) hist[i] = 0u;
   __syncthreads();
   if (HAS_MAP) {
-    for_each_in_chunk<true>(
+    for_each_in_chunk<true, T>(
         chunk, [](float) { return true; },
         [&](float x, int32_t idx) { atomicAdd(&hist[(idx < 0 ? 0u : key_of(x)) >> kFirstShift], 1u); });
   } else {
@@ -1166,11 +1231,10 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       for (int j = 0; j < kTileUnits / kThreads; ++j) {
         const int lu = tid + j * kThreads;
         if (lu < units) {
-          const float4 v = lds_f4(tile + 16u * static_cast<uint32_t>(lu));
-          atomicAdd(&hist[raw_digit(v.x)], 1u);
-          atomicAdd(&hist[raw_digit(v.y)], 1u);
-          atomicAdd(&hist[raw_digit(v.z)], 1u);
-          atomicAdd(&hist[raw_digit(v.w)], 1u);
+          float v[kPU];
+          unpack_unit<T>(lds_u4(tile + 16u * static_cast<uint32_t>(lu)), v);
+#pragma unroll
+          for (int e = 0; e < kPU; ++e) atomicAdd(&hist[raw_digit(v[e])], 1u);
         }
       }
     });
@@ -1234,7 +1298,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (!HAS_MAP && level == 0 && final_level && (static_cast<uint32_t>(t) << kFirstShift) <= 0xff800000u) {
       const float vmin = prefilter_value(static_cast<uint32_t>(t) << kFirstShift);
       stream_pass(ts, [&](uint32_t tile, int tt, int units) {
-        collect_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, stage, kSortCap, &sh.stage_count);
+        collect_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, stage, kSortCap, &sh.stage_count);
       });
       float x = 0.f;
       const int pos = partial_element(chunk, x);
@@ -1259,7 +1323,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         }
       };
       stream_pass(ts, [&](uint32_t tile, int tt, int units) {
-        scan_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
+        scan_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
       });
       float x = 0.f;
       const int pos = partial_element(chunk, x);
@@ -1279,7 +1343,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
           push_aggregated(stage, &sh.stage_count, kSortCap, make_comp(key, pos));
       };
       stream_pass(ts, [&](uint32_t tile, int tt, int units) {
-        scan_tile(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
+        scan_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, vmin, on_hit);
       });
       float x = 0.f;
       const int pos = partial_element(chunk, x);
@@ -1293,7 +1357,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     } else {
       // Everything of interest has composite >= Pn << shift, i.e. value >= vmin.
       const float vmin = prefilter_value(static_cast<uint32_t>((Pn << shift) >> 32));
-      for_each_in_chunk<HAS_MAP>(
+      for_each_in_chunk<HAS_MAP, T>(
           chunk, [vmin](float x) { return !(x < vmin); },
           [&](float x, int32_t idx) { classify_value<HAS_MAP>(&ctx, x, idx); });
     }
@@ -1357,8 +1421,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     }
     return;
   }
-  const int T = min(expected_total, kSortCap);
-  const int hint_rank = min(T, hint_target_rank(k)) - 1;
+  const int n_surv = min(expected_total, kSortCap);
+  const int hint_rank = min(n_surv, hint_target_rank(k)) - 1;
   if (my_share == 0 && tid == 0 && sh.sort_count != expected_total && p.status != nullptr)
     atomicOr(p.status, 1);
 
@@ -1366,7 +1430,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // With n CTAs on the row, CTA s owns the survivors i = s, s + n, ...  When that is at most 32
   // of them (rows split over many clusters), the CTA's threads simply count the
   // survivors above it in this CTA's copy of the list: no histogram, scan or scatter.
-  if (T <= 32 * n_share) {
+  if (n_surv <= 32 * n_share) {
     // Register blocking: a group of 64 lanes (two warps) holds four owned survivors per lane and
     // streams the list once for all four, so shared memory is read half as often as it is compared.
     uint32_t* cnt_arr = reinterpret_cast<uint32_t*>(smem + kSmemRing + 1024);   // [32] ranks
@@ -1377,12 +1441,12 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int idx = my_share + (grp * 4 + e) * n_share;
-      own[e] = idx < T ? sortbuf[idx] : ~0ull;
+      own[e] = idx < n_surv ? sortbuf[idx] : ~0ull;
       part[e] = 0;
     }
     __syncthreads();
 #pragma unroll 2
-    for (int q = l64; q < T; q += 64) {
+    for (int q = l64; q < n_surv; q += 64) {
       const uint64_t o = sortbuf[q];
 #pragma unroll
       for (int e = 0; e < 4; ++e) part[e] += o > own[e] ? 1 : 0;
@@ -1395,18 +1459,18 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     __syncthreads();
     // threads 0..31 finish one owned survivor each
     const int i = my_share + tid * n_share;
-    const bool valid = tid < 32 && i < T;
+    const bool valid = tid < 32 && i < n_surv;
     const uint64_t c = valid ? sortbuf[i] : ~0ull;
     const int cnt = valid ? static_cast<int>(cnt_arr[tid]) : 0;
     if (valid && cnt < k)
       emit<kPush>(p, push, row, cnt, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
     if (kHinted && !HAS_MAP && p.hint_out != nullptr) {
-      // Next call's guess: the score of rank min(T, target) - 1 (hint_target_rank), written by its owner.  With fewer
+      // Next call's guess: the score of rank min(n_surv, target) - 1 (hint_target_rank), written by its owner.  With fewer
       // than `target` survivors that is the smallest one; its owner then extrapolates linearly below
-      // it with the owned survivor whose rank is nearest to T/2 (ranks of the others are not known here).
-      uint32_t* mid = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [32][3]: |rank - T/2|, value bits, rank
+      // it with the owned survivor whose rank is nearest to n_surv/2 (ranks of the others are not known here).
+      uint32_t* mid = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [32][3]: |rank - n_surv/2|, value bits, rank
       if (tid < 32) {
-        mid[3 * tid] = valid ? static_cast<uint32_t>(abs(cnt - (T >> 1))) : 0x7fffffffu;
+        mid[3 * tid] = valid ? static_cast<uint32_t>(abs(cnt - (n_surv >> 1))) : 0x7fffffffu;
         mid[3 * tid + 1] = bits_of_key(comp_key(c));
         mid[3 * tid + 2] = static_cast<uint32_t>(cnt);
       }
@@ -1415,14 +1479,14 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         const float va = __uint_as_float(bits_of_key(comp_key(c)));
         float guess = va;
         const int want = hint_target_rank(k);
-        if (T < want) {
+        if (n_surv < want) {
           int best = 0;
           for (int g = 1; g < 32; ++g)
             if (mid[3 * g] < mid[3 * best]) best = g;
           const float vm = __uint_as_float(mid[3 * best + 1]);
           const int gap = hint_rank - static_cast<int>(mid[3 * best + 2]);   // ranks between the two
-          if (mid[3 * best] < static_cast<uint32_t>(T >> 2) && gap > 0) {
-            const float lower = va - (vm - va) * (static_cast<float>(want - T) / static_cast<float>(gap));
+          if (mid[3 * best] < static_cast<uint32_t>(n_surv >> 2) && gap > 0) {
+            const float lower = va - (vm - va) * (static_cast<float>(want - n_surv) / static_cast<float>(gap));
             if (lower == lower && fabsf(lower) <= 3.0e38f) guess = lower;
           }
         }
@@ -1433,7 +1497,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     return;
   }
 
-  // ---- finish: rank the T survivors and write the first k ------------------
+  // ---- finish: rank the n_surv survivors and write the first k ------------------
   // A counting sort on an adaptive linear digit: bin = (comp - floor) >> shift
   // with shift chosen so the survivors' composite range spans <= 4096 bins (any
   // monotone bin map keeps the result exact).  Every CTA builds the same
@@ -1454,7 +1518,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // index half too when every key is equal (then only the indices separate them)
   uint32_t hmax = 0u, hmin = 0xffffffffu, lmax = 0u, lmin = 0xffffffffu;
 #pragma unroll 1
-  for (int i = tid; i < T; i += kThreads) {
+  for (int i = tid; i < n_surv; i += kThreads) {
     const uint64_t c = sortbuf[i];
     hmax = max(hmax, static_cast<uint32_t>(c >> 32));
     hmin = min(hmin, static_cast<uint32_t>(c >> 32));
@@ -1475,7 +1539,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid; i < kPadBins; i += kThreads) fh[i] = 0u;
 #pragma unroll 1
-  for (int i = tid; i < T; i += kThreads) rankcnt[i] = 0u;
+  for (int i = tid; i < n_surv; i += kThreads) rankcnt[i] = 0u;
   if (tid == 0) {
     sh.small_count = 0;
     sh.big_count = 0;
@@ -1495,7 +1559,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const int bshift = nbits > 12 ? nbits - 12 : 0;
   // arrival order inside the bin doubles as the scatter offset
 #pragma unroll 1
-  for (int i = tid; i < T; i += kThreads) {
+  for (int i = tid; i < n_surv; i += kThreads) {
     const uint32_t b = static_cast<uint32_t>((sortbuf[i] - lo) >> bshift);
     at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
   }
@@ -1518,7 +1582,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   __syncthreads();
   FF_TRACE(p, 23);
 #pragma unroll 1
-  for (int i = tid; i < T; i += kThreads) {
+  for (int i = tid; i < n_surv; i += kThreads) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const uint32_t at = E[b] + at_arr[i];
@@ -1535,7 +1599,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   constexpr uint32_t kUnitBucket = 32u;
   uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 98 * 1024);   // slots, <= kSortCap
 #pragma unroll 1
-  for (int i = tid * n_share + my_share; i < T; i += kThreads * n_share) {
+  for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     if (static_cast<int>(E[b]) >= k) continue;
@@ -1591,7 +1655,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   }
   __syncthreads();
 #pragma unroll 1
-  for (int i = tid * n_share + my_share; i < T; i += kThreads * n_share) {
+  for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
@@ -1600,12 +1664,12 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // Next call's guess: a score of rank hint_target_rank(k), so that about that many elements (between k and
   // 4096) pass it on similar data.  With at least that many survivors it is the lower edge of the bucket
   // that holds that rank; with fewer it is extrapolated linearly below the smallest survivor
-  // from the ranks T/2 and T.  Two lanes of the row's first CTA each find one bucket by a
+  // from the ranks n_surv/2 and n_surv.  Two lanes of the row's first CTA each find one bucket by a
   // binary search over the buckets' suffix counts (the same in every CTA).
   if (kHinted && !HAS_MAP && p.hint_out != nullptr && my_share == 0 && tid < 32) {
     const int want = hint_target_rank(k);
-    const int rank_a = min(T, want) - 1;
-    const int rank_m = T >> 1;
+    const int rank_a = min(n_surv, want) - 1;
+    const int rank_m = n_surv >> 1;
     const int rank_mine = (tid & 1) ? rank_m : rank_a;
     int b_lo = 0, b_hi = kFinishBins - 1;   // largest bucket b with #(bins >= b) > rank
 #pragma unroll 1
@@ -1620,7 +1684,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const float vm = __shfl_sync(0xffffffffu, v_mine, 1);
     if (tid == 0) {
       float guess = va;
-      if (T < want && rank_a > rank_m) {
+      if (n_surv < want && rank_a > rank_m) {
         const float lower = va - (vm - va) * (static_cast<float>(want - 1 - rank_a) / static_cast<float>(rank_a - rank_m));
         if (lower == lower && fabsf(lower) <= 3.0e38f) guess = lower;   // finite
       }
@@ -1630,11 +1694,11 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   FF_TRACE(p, 25);
 }
 
-template <bool HAS_MAP, int MODE>
-__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
+// One CTA's whole job for one rank: the row body, and in context-parallel send mode the step
+// counter and (single-kernel step) the merge of the row's candidates from all ranks.
+template <bool HAS_MAP, int MODE, typename T>
+__device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* smem, ClusterShared& sh) {
   constexpr bool kPush = (MODE & kModePush) != 0;
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ ClusterShared sh;
   // Context-parallel send: this launch also delivers its result to the peers.  The step number is
   // read from device memory (graph replays), the slot it selects is fixed for the whole launch.
   PushCtx push;
@@ -1646,35 +1710,48 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
     push.step = *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) + 1u;
     push.off = (static_cast<int64_t>(push.step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
   }
-  topk_row_body<HAS_MAP, MODE>(p, smem, sh, push);
+  topk_row_body<HAS_MAP, MODE, T>(p, smem, sh, push);
   if (kPush && !HAS_MAP && p.push_world > 0) {
+    FF_TRACE(p, 32);
     // Every CTA read the step long ago; the one that counts itself last advances the counter.
     // A thread outside warp 0 does it, so that its round trip overlaps the merge below.
     if (threadIdx.x == 32) {
-      if (atomicAdd(ctrl + kPushDoneWord, 1u) == gridDim.x - 1u) {
+      if (atomicAdd(ctrl + kPushDoneWord, 1u) == static_cast<uint32_t>(p.grid_ctas) - 1u) {
         ctrl[kPushDoneWord] = 0u;
         __threadfence();
         *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) = push.step;
       }
     }
     if (p.push_fused != 0) {
-      // Single-kernel step: merge this row's world x k candidates right here.  The row's CTAs
-      // share them out (at least one per thread); each stages all run keys in shared memory,
-      // polling every entry until it carries this step, and ranks its share by binary searches.
-      // All CTAs of the launch are resident at once (checked by the host), so a CTA that polls
-      // cannot keep a CTA that has yet to store its entries from running.
+      // Single-kernel step: merge this row's candidates right here.  All CTAs of the launch are
+      // resident at once (cooperative launch), so a CTA that polls cannot keep a CTA that has
+      // yet to store its entries from running.
+      //
+      // Round 1 works on the PREFIXES: the first S = push_prefix candidates of every rank's run,
+      // which is all the peers were sent.  The row's first CTAs share those world x S candidates
+      // out (at least one per thread); each stages all prefix keys in shared memory, polling
+      // every entry until it carries this step, and ranks its share by binary searches.  The
+      // prefixes hold the row's whole top-k exactly when, for every rank, the LAST candidate of
+      // its prefix is not among the first k of the merged prefixes (then nothing behind it can
+      // be either).  Every merging CTA of every rank checks that itself on the same keys, so all
+      // reach the same verdict without talking to each other.
+      // Round 2 (rare: most winners in few shards): every rank's merging CTAs send the rest of
+      // their own run to the peers, and the merge is redone on the full runs.
       cg::cluster_group cluster = cg::this_cluster();
       const int C = static_cast<int>(cluster.num_blocks());
       const int G = max(p.groups, 1);
-      const int row = static_cast<int>(blockIdx.x) / (C * G);
+      const int bid = static_cast<int>(blockIdx.x) - p.block_base;
+      const int row = bid / (C * G);
       const int n_share = C * G;
-      const int my_share = (static_cast<int>(blockIdx.x) / C) % G * C + static_cast<int>(cluster.block_rank());
+      const int my_share = (bid / C) % G * C + static_cast<int>(cluster.block_rank());
       const int k = p.k;
       const int world = p.push_world;
+      const int S = min(max(p.push_prefix, 1), k);
       const int glen = p.lengths[row];
-      const int n_cand = world * k;
+      const int n_cand = world * S;
       int per = (n_cand + n_share - 1) / n_share;
       if (per < kThreads) per = kThreads;
+      const int n_merge = (n_cand + per - 1) / per;   // CTAs of the row that merge
       const int begin = my_share * per;
       int32_t* out_row = p.out_idx + static_cast<int64_t>(row) * k;
       if (glen <= k) {   // short row: identity order, as everywhere else
@@ -1685,14 +1762,62 @@ __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkPar
         src.base = p.push_peers.base[p.push_rank] + static_cast<int64_t>(push.step & 1u) * world * p.push_slot_words;
         src.slot_words = p.push_slot_words;
         src.row_words = 4 * static_cast<int64_t>(row) * k;
-        uint32_t* run_keys = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [world][k], at most 128 KiB
+        uint32_t* run_keys = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [world][S] or [world][k], at most 128 KiB
         __syncthreads();   // the ring region is free in the whole CTA
-        bool ok = stage_run_keys(src, world, k, push.step, run_keys);
-        ok = rank_and_write(src, run_keys, world, k, push.step, begin, min(n_cand, begin + per), out_row) && ok;
+        bool ok = stage_run_keys(src, world, k, S, push.step, run_keys);
+        FF_TRACE(p, 33);
+        const bool enough = S >= k || prefixes_suffice(run_keys, world, S, k);
+        FF_TRACE(p, 34);
+        if (enough) {
+          ok = rank_and_write(src, run_keys, world, k, S, push.step, begin, min(n_cand, begin + per), out_row) && ok;
+        } else {
+          // the rest of this rank's run: from its own slot to every peer, shared out over the merging CTAs
+          const unsigned long long t0 = global_ns();
+          for (int j = S + my_share * kThreads + static_cast<int>(threadIdx.x); j < k; j += n_merge * kThreads) {
+            const uint32_t* ve = src.value_entry(p.push_rank, j);
+            const uint32_t vbits = await_entry(ve, ld_entry(ve), push.step, t0, ok);
+            const uint32_t gidx = await_entry(ve + 2, ld_entry(ve + 2), push.step, t0, ok);
+            if (ok) {
+              const size_t at = push.off + 4 * (static_cast<size_t>(row) * k + j);
+              for (int q = 0; q < world; ++q)
+                if (q != p.push_rank) st_entry(p.push_peers.base[q] + at, vbits, gidx, push.step);
+            }
+          }
+          __syncthreads();   // the prefix keys are not needed any more
+          ok = stage_run_keys(src, world, k, k, push.step, run_keys) && ok;
+          const int all = world * k;
+          const int slice = (all + n_merge - 1) / n_merge;
+          ok = rank_and_write(src, run_keys, world, k, k, push.step, my_share * slice, min(all, (my_share + 1) * slice),
+                              out_row) && ok;
+          if (p.status != nullptr && threadIdx.x == 0 && my_share == 0) atomicOr(p.status, 16);
+        }
+        FF_TRACE(p, 35);
         if (!ok && p.status != nullptr) atomicOr(p.status, 2);
       }
     }
   }
+}
+
+template <bool HAS_MAP, int MODE, typename T = float>
+__global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ ClusterShared sh;
+  topk_cta<HAS_MAP, MODE, T>(p, smem, sh);
+}
+
+// Several ranks of a context-parallel step played by ONE cooperative launch on one GPU (for
+// tests on a box with fewer GPUs than ranks: kernels that wait for one another must never be
+// separate launches on one device).  Rank r owns the CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank).
+constexpr int kMaxEmulatedRanks = 8;
+struct EmulatedRanks {
+  TopkParams rank[kMaxEmulatedRanks];
+  int32_t ctas_per_rank;
+};
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1) topk_emulated_ranks_kernel(const __grid_constant__ EmulatedRanks e) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ ClusterShared sh;
+  topk_cta<false, MODE, float>(e.rank[blockIdx.x / e.ctas_per_rank], smem, sh);
 }
 
 }  // namespace ff

@@ -35,7 +35,7 @@ CASES = {
 
 
 def trace_once(score, lengths, k, cluster=0, hinted=False):
-    """Returns (cluster_size, int64 array [n_ctas, 32] of cycle stamps).  With ``hinted`` the
+    """Returns (cluster_size, int64 array [n_ctas, TRACE_SLOTS] of cycle stamps).  With ``hinted`` the
     warm-up launches leave a threshold guess per row and the traced launch uses it (no histogram
     stages then)."""
     lib = _lib.load()
@@ -46,7 +46,7 @@ def trace_once(score, lengths, k, cluster=0, hinted=False):
     lib.ff_topk_policy_launch_shape(score.shape[0], score.shape[1], k, 1, 1 if hinted else 0, shape)
     C = int(shape[0])            # CTAs per cluster of the launch actually made (a row may span shape[1] clusters)
     # a row may be split over up to 64 clusters of up to 16 CTAs: size the buffer for the largest grid
-    buf = torch.zeros((score.shape[0] * 1024, 32), dtype=torch.int64, device=dev)
+    buf = torch.zeros((score.shape[0] * 1024, _lib.TRACE_SLOTS), dtype=torch.int64, device=dev)
     out = torch.empty((score.shape[0], k), dtype=torch.int32, device=dev)
     hint = None
     if hinted:

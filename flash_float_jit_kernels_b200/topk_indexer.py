@@ -61,11 +61,14 @@ def _workspace(lib, device: torch.device, B: int, L: int, k: int, stream: Option
     return ws, ws.numel()
 
 
-def _check_common(score, lengths, topk, row_starts):
+_SCORE_DTYPES = {torch.float32: _lib.FF_DTYPE_F32, torch.bfloat16: _lib.FF_DTYPE_BF16, torch.float16: _lib.FF_DTYPE_F16}
+
+
+def _check_common(score, lengths, topk, row_starts, dtypes=(torch.float32,)):
     _require(isinstance(topk, int) and 1 <= topk <= _lib.FF_TOPK_MAX_K,
              f"fast_topk_v3 supports topk in [1, {_lib.FF_TOPK_MAX_K}], got {topk}")
     _require(score.dim() == 2, "score must be 2-D [B, L]")
-    _require(score.dtype == torch.float32, "score must be float32")
+    _require(score.dtype in dtypes, "score must be " + " or ".join(str(d).replace("torch.", "") for d in dtypes))
     _require(score.is_cuda, "score must be a CUDA tensor (there is no CPU path)")
     _require(score.size(1) == 0 or score.stride(1) == 1, "score.stride(1) must be 1")
     B = score.size(0)
@@ -89,18 +92,24 @@ def fast_topk_v3(
     out: Optional[torch.Tensor] = None,
     status: Optional[torch.Tensor] = None,
     threshold_hint: Optional[torch.Tensor] = None,
+    index_dtype: torch.dtype = torch.int32,
 ) -> torch.Tensor:
     """Top-k indices of every row of ``score`` (reference: ``topk_indexer.py:109``).
 
     Args:
-        score: (B, L) float32 CUDA tensor, ``stride(1) == 1``, any row stride.
+        score: (B, L) float32 CUDA tensor, ``stride(1) == 1``, any row stride.  bfloat16 and
+            float16 scores are accepted as well (extension; the reference is fp32 only): each
+            value is widened to fp32 exactly, so the result is that of the fp32 row with the
+            same values, and half the bytes are read.
         lengths: (B) int32 valid length per row.
         topk: number of indices per row, 1..2048 (the reference accepts
             512, 1024 and 2048 only).
         row_starts: optional (B) int32 window start per row; returned indices
             are relative to the window.
-        out: optional preallocated (B, topk) int32 result (extension; lets a
+        out: optional preallocated (B, topk) int32 or int64 result (extension; lets a
             caller keep the call allocation-free inside a CUDA graph).
+        index_dtype: ``torch.int32`` (default, as the reference) or ``torch.int64`` (the
+            layout ``torch.topk`` returns) for the result when ``out`` is not given.
         status: optional int32 device scalar that collects soft-error bits.
         threshold_hint: optional (B) float32 device tensor, read AND updated
             (extension; see :func:`new_threshold_hint`).  Entry ``i`` is a guess
@@ -116,14 +125,16 @@ def fast_topk_v3(
         (B, topk) int32 indices in (value desc, index asc) order, ``-1``
         padded for rows shorter than ``topk``.
     """
-    _check_common(score, lengths, topk, row_starts)
+    _check_common(score, lengths, topk, row_starts, dtypes=tuple(_SCORE_DTYPES))
     lib = _lib.load()
     B, L = score.size(0), score.size(1)
     if out is None:
-        out = torch.empty((B, topk), dtype=torch.int32, device=score.device)
+        _require(index_dtype in (torch.int32, torch.int64), "index_dtype must be torch.int32 or torch.int64")
+        out = torch.empty((B, topk), dtype=index_dtype, device=score.device)
     else:
-        _require(out.shape == (B, topk) and out.dtype == torch.int32 and out.is_contiguous()
-                 and out.device == score.device, "out must be a contiguous (B, topk) int32 tensor")
+        _require(out.shape == (B, topk) and out.dtype in (torch.int32, torch.int64) and out.is_contiguous()
+                 and out.device == score.device, "out must be a contiguous (B, topk) int32 or int64 tensor")
+    typed = score.dtype != torch.float32 or out.dtype != torch.int32
     if B == 0:
         return out
     dev = score.device
@@ -136,6 +147,12 @@ def fast_topk_v3(
                  "threshold_hint must be a contiguous (B) float32 tensor on score's device")
 
     def call():
+        if typed:
+            hint_ptr = None if threshold_hint is None else threshold_hint.data_ptr()
+            return lib.ff_topk_launch_typed(
+                score.data_ptr(), _SCORE_DTYPES[score.dtype], row_stride, lengths.data_ptr(), _ptr(row_starts),
+                out.data_ptr(), 64 if out.dtype == torch.int64 else 32, B, L, topk, hint_ptr, hint_ptr,
+                _ptr(ws), ws_bytes, _ptr(status), stream)
         if threshold_hint is None:
             return lib.ff_topk_launch(
                 score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,

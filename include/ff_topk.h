@@ -44,6 +44,8 @@ extern "C" {
 #define FF_STATUS_WAIT_TIMEOUT 2   /* a bounded cross-cluster wait ran out    */
 #define FF_STATUS_NO_THRESHOLD 4   /* no threshold digit found (corrupt hist) */
 #define FF_STATUS_HINT_MISSED 8    /* information, not an error: a threshold guess did not fit */
+#define FF_STATUS_CP_SECOND_ROUND 16 /* information, not an error: a context-parallel step needed the ranks' whole
+                                        candidate runs, not only their first part (winners crowded into few shards) */
 
 /* Output epilogue applied to each selected window-relative index `p`
  * (reference: topk_indexer_radix.cu:1000-1124, the fused page-table
@@ -108,6 +110,21 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
 int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t* lengths,
                           const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
                           int32_t k, int32_t* status, void* stream);
+
+/* ff_topk_launch for other score and index types (no reference counterpart: the reference is fp32
+ * with int32 indices only and leaves a half-precision value type commented out,
+ * topk_indexer_radix.cu:563-564).  score_dtype says what `scores` points to; row_stride counts
+ * elements of that type.  A 16-bit score is widened to fp32 exactly, so the result is the one
+ * ff_topk_launch gives for the fp32 row with the same values, while half the bytes are read.
+ * index_bits = 64 makes out_idx an int64_t [B, k] array (the layout torch.topk returns), else 32.
+ * hint_in / hint_out as in ff_topk_launch_hinted (both may be NULL). */
+#define FF_DTYPE_F32 0
+#define FF_DTYPE_BF16 1
+#define FF_DTYPE_F16 2
+int ff_topk_launch_typed(const void* scores, int32_t score_dtype, int64_t row_stride, const int32_t* lengths,
+                         const int32_t* row_starts, void* out_idx, int32_t index_bits, int32_t B, int64_t L_width,
+                         int32_t k, const float* hint_in, float* hint_out, void* workspace, size_t workspace_bytes,
+                         int32_t* status, void* stream);
 
 /* ff_topk_launch with a threshold guess per row (no reference counterpart: the
  * reference only discusses reusing the previous decode step's threshold,
@@ -180,7 +197,12 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
  *   ff_topk_cp_send            shard-local select whose epilogue stores into all peers (1 launch)
  *   ff_topk_cp_recv_merge      wait for all peers' entries of the current step + merge (1 launch)
  *   ff_topk_cp_step            the whole step as ONE launch (select, store to peers, poll, merge) when
- *                              all CTAs of the launch can be resident at once; else send + recv_merge
+ *                              all CTAs of the launch can be resident at once; else send + recv_merge.
+ *                              In the one-launch form with more than two ranks a rank first sends only the
+ *                              head of its run (2k/world candidates per row, at least 256; FF_TOPK_CP_PREFIX
+ *                              overrides): the heads hold the row's whole top-k unless some head is used up
+ *                              entirely, which every rank detects on the same data; then all ranks send the
+ *                              rest and merge the whole runs (FF_STATUS_CP_SECOND_ROUND, exact either way)
  *   ff_topk_cp_send_hinted / ff_topk_cp_step_hinted
  *                              the same with threshold guesses for the shard-local select: hint_in /
  *                              hint_out are [B] floats of THIS rank's shard, with the meaning and the
@@ -212,13 +234,25 @@ int ff_topk_cp_step_hinted(void* handle, const float* scores, int64_t row_stride
                            float* hint_out, void* workspace, size_t workspace_bytes, int32_t* status,
                            void* stream);
 
+/* Test hook (no reference counterpart): n_ranks <= 8 ranks of a context-parallel step played by ONE
+ * cooperative launch on the current GPU, for boxes with fewer GPUs than ranks (kernels that wait for
+ * one another must not be separate launches on one device).  handles[r] is rank r's exchange (peers set
+ * with ff_cp_exchange_set_peer), scores[r] / L_width[r] / shard_offset[r] its shard, out_idx[r] its
+ * [B, k] result, hints[r] (array or entries may be NULL) its [B] threshold guesses, read and updated,
+ * workspaces[r] its zero-filled scratch of workspace_bytes each (may be NULL).  All shards must get the
+ * same launch shape.  Same kernel code and protocol as ff_topk_cp_step_hinted on real ranks. */
+int ff_topk_cp_step_emulated_ranks(int32_t n_ranks, void* const* handles, const float* const* scores,
+                                   int64_t row_stride, const int32_t* lengths, int32_t* const* out_idx,
+                                   const int64_t* L_width, const int64_t* shard_offset, float* const* hints,
+                                   void* const* workspaces, size_t workspace_bytes, int32_t* status, void* stream);
+
 /* Test / tuning hook: force the thread-block-cluster size per row
  * (0 = automatic policy, else 1, 2, 4, 8 or 16).  Process-wide. */
 int ff_topk_set_cluster_override(int32_t cluster_size);
 
 /* Debug aid: when non-NULL, every CTA of every later launch writes its stage
- * time stamps (SM cycle counter) to device_buffer[cta * 32 + slot] (uint64).
- * The buffer must hold 32 words per CTA of the largest launch.  Process-wide;
+ * time stamps (SM cycle counter) to device_buffer[cta * 40 + slot] (uint64).
+ * The buffer must hold 40 words per CTA of the largest launch.  Process-wide;
  * pass NULL to switch tracing off.  Plays the role of the reference's
  * SMALL_K_PROFILE clock64 brackets (top_small_k.cuh:39-41,132-135). */
 int ff_topk_set_trace_buffer(void* device_buffer);

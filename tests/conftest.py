@@ -23,7 +23,10 @@ def golden():
         cases[n] = dict(
             score=z[f"{n}/score"], lengths=z[f"{n}/lengths"], k=int(z[f"{n}/k"]),
             row_starts=z[f"{n}/row_starts"] if f"{n}/row_starts" in z.files else None,
-            expected=z[f"{n}/expected"])
+            expected=z[f"{n}/expected"],
+            # 16-bit cases: the raw bits and "bf16" / "f16"; "score" is then their exact fp32 widening
+            bits16=z[f"{n}/score_bits16"] if f"{n}/score_bits16" in z.files else None,
+            dtype=str(z[f"{n}/dtype"]) if f"{n}/dtype" in z.files else "f32")
     return cases
 
 

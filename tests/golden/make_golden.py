@@ -82,6 +82,23 @@ def main():
     x[2, :] = torch.randint(0, 4, (2048,), generator=g).float()
     add("special_values_k64", x, torch.tensor([2048, 2048, 2000], dtype=torch.int32), 64)
     add("special_values_k1000", x, torch.tensor([2048, 2048, 2000], dtype=torch.int32), 1000)
+    # 16-bit scores: the expected result is the stable sort of the 16-bit tensor ITSELF; the stored
+    # "score" is its exact fp32 widening (what the oracle statements read), "score_bits16" the raw bits
+    for tag, dt in (("bf16", torch.bfloat16), ("f16", torch.float16)):
+        g = torch.Generator().manual_seed(105)
+        x16 = torch.randn((3, 6000), generator=g).to(dt)
+        x16[1, 100:200] = 0.0
+        x16[1, 150:180] = -0.0
+        x16[2, 7] = float("inf")
+        x16[2, 8] = float("nan")
+        lengths = torch.tensor([6000, 5999, 3001], dtype=torch.int32)
+        rs = torch.tensor([0, 1, 2999], dtype=torch.int32)          # odd window starts: misaligned 16-byte units
+        for name, k, r in ((f"{tag}_6000_k512", 512, None), (f"{tag}_6000_rs_k1000", 1000, rs)):
+            exp = expected(x16, lengths if r is None else torch.tensor([6000, 5999, 3001], dtype=torch.int32), k, r)
+            add(name, x16.float(), lengths, k, r)
+            assert np.array_equal(cases[f"{name}/expected"], exp.numpy()), "widening changed the order"
+            cases[f"{name}/score_bits16"] = x16.view(torch.int16).numpy()
+            cases[f"{name}/dtype"] = np.array(tag)
     out = Path(__file__).resolve().parent / "topk_golden.npz"
     np.savez_compressed(out, **cases)
     print(out, out.stat().st_size, "bytes", len([c for c in cases if c.endswith('/k')]), "cases")

@@ -384,3 +384,141 @@ def test_single_kernel_step_with_threshold_guesses(oracle):
         finally:
             torch.cuda.synchronize()
             lib.ff_cp_exchange_destroy(h)
+
+
+# ---- several ranks in ONE launch: the single-kernel step with world > 1 on one GPU -----------
+def _emulated_shape(P, B):
+    """(cluster size, clusters per row) such that the CTAs of all P ranks are resident together
+    (a B200 holds 15 clusters of 8 or about 36 of 4 of this kernel)."""
+    if P == 2 and B == 1:
+        return 8, 7
+    return 4, max(2, 28 // (P * B))
+
+
+def _emulated_step(lib, exs, shards, lengths_dev, outs, offsets, hints, wss, ws_bytes, status):
+    import ctypes
+    P = len(exs)
+    vp = ctypes.c_void_p * P
+    i64 = ctypes.c_int64 * P
+    return lib.ff_topk_cp_step_emulated_ranks(
+        P, vp(*[h.value for h in exs]), vp(*[s.data_ptr() for s in shards]), shards[0].stride(0),
+        lengths_dev.data_ptr(), vp(*[o.data_ptr() for o in outs]), i64(*[s.size(1) for s in shards]), i64(*offsets),
+        None if hints is None else vp(*[h.data_ptr() for h in hints]), vp(*[w.data_ptr() for w in wss]), ws_bytes,
+        status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+
+
+def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=False, expect_second_round=None):
+    """Plays P ranks of `steps` context-parallel steps in one launch each and compares every
+    rank's result with the oracle on the unsharded rows.  Returns the status word of every step."""
+    from flash_float_jit_kernels_b200 import _lib, new_threshold_hint, shard_bounds
+    lib = _lib.load()
+    dev = torch.device("cuda:0")
+    cluster, groups = _emulated_shape(P, B)
+    assert L % (4 * P) == 0, "equal shards, so that every rank gets the same launch shape"
+    if prefix is not None:
+        os.environ["FF_TOPK_CP_PREFIX"] = str(prefix)
+    lib.ff_topk_set_cluster_override(cluster)
+    lib.ff_topk_set_groups_override(groups)
+    exs = _make_exchanges(lib, P, B, k)
+    seen = []
+    try:
+        ws_bytes = int(lib.ff_topk_workspace_bytes(B, L // P, k))
+        assert ws_bytes > 0
+        wss = [torch.zeros(ws_bytes, dtype=torch.uint8, device=dev) for _ in range(P)]
+        hints = [new_threshold_hint(B, dev) for _ in range(P)] if use_hints else None
+        outs = [torch.full((B, k), -5, dtype=torch.int32, device=dev) for _ in range(P)]
+        for step in range(steps):
+            s, lengths = make_row(step)
+            sd, ld = s.to(dev), lengths.to(dev)
+            shards, offsets = [], []
+            for r in range(P):
+                a, b = shard_bounds(L, P, r)
+                shards.append(sd[:, a:b])
+                offsets.append(a)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            launches = lib.ff_topk_launch_count()
+            rc = _emulated_step(lib, exs, shards, ld, outs, offsets, hints, wss, ws_bytes, status)
+            assert rc == 0, lib.ff_last_error_string()
+            assert lib.ff_topk_launch_count() - launches == 1
+            torch.cuda.synchronize()
+            bits = int(status.item())
+            seen.append(bits)
+            assert bits & ~(_lib.FF_STATUS_HINT_MISSED | _lib.FF_STATUS_CP_SECOND_ROUND) == 0, f"step {step}: status {bits}"
+            if expect_second_round is not None:
+                assert bool(bits & _lib.FF_STATUS_CP_SECOND_ROUND) == expect_second_round, f"step {step}: status {bits}"
+            exp = oracle.topk_c(s.numpy(), lengths.numpy(), k)
+            for r in range(P):
+                assert np.array_equal(outs[r].cpu().numpy(), exp), f"step {step} rank {r}"
+    finally:
+        torch.cuda.synchronize()
+        os.environ.pop("FF_TOPK_CP_PREFIX", None)
+        lib.ff_topk_set_cluster_override(0)
+        lib.ff_topk_set_groups_override(0)
+        for h in exs:
+            lib.ff_cp_exchange_destroy(h)
+    return seen
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+@pytest.mark.parametrize("ties", [False, True])
+def test_single_kernel_step_with_several_ranks_in_one_launch(oracle, P, ties):
+    """world > 1 in the one-launch form: i.i.d. rows, so the heads of the runs (2k / world
+    candidates per rank) hold the whole top-k and no second round is taken."""
+    B, L, k = 1, 1 << 20, 2048
+
+    def make_row(step):
+        s = torch.randn((B, L), generator=torch.Generator().manual_seed(4000 + 10 * P + step))
+        if ties:
+            s = s.to(torch.bfloat16).float()
+        return s, torch.tensor([L - 4321 * step], dtype=torch.int32)
+
+    _run_emulated(oracle, P, B, L, k, make_row, steps=3, expect_second_round=False)
+
+
+@pytest.mark.parametrize("P", [4, 8])
+def test_second_round_when_the_winners_crowd_into_one_shard(oracle, P):
+    """A row that rises towards its end has its whole top-k in the last shard: the heads of the
+    runs are not enough, every rank sees that on the same keys, and the ranks exchange the rest."""
+    B, L, k = 1, 1 << 19, 1024
+
+    def make_row(step):
+        g = torch.Generator().manual_seed(4100 + step)
+        s = torch.randn((B, L), generator=g) + torch.linspace(0.0, 40.0, L).unsqueeze(0)
+        if step == 1:        # equal scores everywhere: the lowest indices win, all in shard 0
+            s = torch.full((B, L), 1.5)
+        return s, torch.tensor([L], dtype=torch.int32)
+
+    seen = _run_emulated(oracle, P, B, L, k, make_row, steps=4, expect_second_round=True)
+    assert all(b & 16 for b in seen)
+
+
+@pytest.mark.parametrize("prefix", [1, 7, 300])
+def test_short_heads_fall_back_to_whole_runs(oracle, prefix):
+    """Forced tiny heads (FF_TOPK_CP_PREFIX): every step needs the second round; two rows, one of
+    them ending inside the second shard and one no longer than k."""
+    P, B, L, k = 4, 2, 1 << 18, 512
+
+    def make_row(step):
+        s = torch.randn((B, L), generator=torch.Generator().manual_seed(4200 + step)).to(torch.bfloat16).float()
+        lengths = torch.tensor([L, (L // P) + 1000 * step + 3], dtype=torch.int32)
+        if step == 2:
+            lengths[1] = 400      # <= k: identity order
+        return s, lengths
+
+    _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=prefix)
+
+
+def test_several_ranks_in_one_launch_with_threshold_guesses(oracle):
+    P, B, L, k = 4, 1, 1 << 20, 2048
+    base = torch.randn((B, L), generator=torch.Generator().manual_seed(4300)).to(torch.bfloat16).float()
+
+    def make_row(step):
+        drift = 0.01 * torch.randn((B, L), generator=torch.Generator().manual_seed(4301 + step))
+        s = (base + drift).to(torch.bfloat16).float()
+        if step == 3:
+            s = s * 4.0 + 10.0
+        return s, torch.tensor([L], dtype=torch.int32)
+
+    seen = _run_emulated(oracle, P, B, L, k, make_row, steps=5, use_hints=True)
+    assert seen[1] == 0 and seen[2] == 0, "guesses from the previous step should hit on drifting rows"
+    assert seen[3] & 8, "the jump makes every shard's guess miss"
