@@ -804,7 +804,9 @@ int ff_topk_cp_recv_merge(void* handle, const int32_t* lengths, int32_t* out_idx
   p.k = ex->k;
   const int n_cand = ex->world * ex->k;
   const dim3 grid((n_cand + 1023) / 1024, ex->B, 1);
-  const size_t key_bytes = static_cast<size_t>(n_cand) * sizeof(uint32_t);   // <= 128 KiB
+  int sp = 1;
+  while (sp < ex->k) sp *= 2;   // runs are staged at a power-of-two length
+  const size_t key_bytes = static_cast<size_t>(ex->world) * sp * sizeof(uint32_t);   // <= 128 KiB
   ff::cp_merge_sorted_kernel<<<grid, 1024, key_bytes, static_cast<cudaStream_t>(stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail_cuda(e, "cp_merge_sorted_kernel");

@@ -1714,14 +1714,10 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
   if (kPush && !HAS_MAP && p.push_world > 0) {
     FF_TRACE(p, 32);
     // Every CTA read the step long ago; the one that counts itself last advances the counter.
-    // A thread outside warp 0 does it, so that its round trip overlaps the merge below.
-    if (threadIdx.x == 32) {
-      if (atomicAdd(ctrl + kPushDoneWord, 1u) == static_cast<uint32_t>(p.grid_ctas) - 1u) {
-        ctrl[kPushDoneWord] = 0u;
-        __threadfence();
-        *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) = push.step;
-      }
-    }
+    // The atomic is issued here and its result is looked at only after the merge below, so its
+    // round trip overlaps the merge instead of delaying it.
+    uint32_t counted_before = 0u;
+    if (threadIdx.x == 32) counted_before = atomicAdd(ctrl + kPushDoneWord, 1u);
     if (p.push_fused != 0) {
       // Single-kernel step: merge this row's candidates right here.  All CTAs of the launch are
       // resident at once (cooperative launch), so a CTA that polls cannot keep a CTA that has
@@ -1749,8 +1745,11 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
       const int S = min(max(p.push_prefix, 1), k);
       const int glen = p.lengths[row];
       const int n_cand = world * S;
+      // kMergePer candidates per merging CTA (one per thread of its first warps): ranking costs
+      // issue slots, so it is spread thin over many CTAs rather than packed into a few
+      constexpr int kMergePer = 128;
       int per = (n_cand + n_share - 1) / n_share;
-      if (per < kThreads) per = kThreads;
+      if (per < kMergePer) per = kMergePer;
       const int n_merge = (n_cand + per - 1) / per;   // CTAs of the row that merge
       const int begin = my_share * per;
       int32_t* out_row = p.out_idx + static_cast<int64_t>(row) * k;
@@ -1764,13 +1763,24 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
         src.row_words = 4 * static_cast<int64_t>(row) * k;
         uint32_t* run_keys = reinterpret_cast<uint32_t*>(smem + kSmemRing);   // [world][S] or [world][k], at most 128 KiB
         __syncthreads();   // the ring region is free in the whole CTA
-        bool ok = stage_run_keys(src, world, k, S, push.step, run_keys);
+        FF_TRACE(p, 36);
+        const int log_sp = log2_ceil(S);
+        bool ok = stage_run_keys(src, world, S, log_sp, push.step, run_keys);
         FF_TRACE(p, 33);
-        const bool enough = S >= k || prefixes_suffice(run_keys, world, S, k);
+        const int end = min(n_cand, begin + per);
+        const bool one_each = per <= kThreads - 32;   // one candidate per thread; the last warp checks the heads meanwhile
+        const int c = one_each ? begin + static_cast<int>(threadIdx.x) : 0;
+        int rank;
+        const bool short_of =
+            rank_share_and_check_heads(run_keys, world, S, log_sp, k, c, one_each ? end : 0, S < k, rank);
+        FF_TRACE(p, 37);
+        const bool enough = S >= k || __syncthreads_or(short_of ? 1 : 0) == 0;
         FF_TRACE(p, 34);
         if (enough) {
-          ok = rank_and_write(src, run_keys, world, k, S, push.step, begin, min(n_cand, begin + per), out_row) && ok;
-        } else {
+          if (one_each) ok = write_winner(src, S, c, rank, k, push.step, global_ns(), out_row) && ok;
+          else ok = rank_and_write(src, run_keys, world, k, S, log_sp, push.step, begin, end, out_row) && ok;
+        }
+        if (!enough) {
           // the rest of this rank's run: from its own slot to every peer, shared out over the merging CTAs
           const unsigned long long t0 = global_ns();
           for (int j = S + my_share * kThreads + static_cast<int>(threadIdx.x); j < k; j += n_merge * kThreads) {
@@ -1784,16 +1794,22 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
             }
           }
           __syncthreads();   // the prefix keys are not needed any more
-          ok = stage_run_keys(src, world, k, k, push.step, run_keys) && ok;
+          const int log_k = log2_ceil(k);
+          ok = stage_run_keys(src, world, k, log_k, push.step, run_keys) && ok;
           const int all = world * k;
           const int slice = (all + n_merge - 1) / n_merge;
-          ok = rank_and_write(src, run_keys, world, k, k, push.step, my_share * slice, min(all, (my_share + 1) * slice),
-                              out_row) && ok;
+          ok = rank_and_write(src, run_keys, world, k, k, log_k, push.step, my_share * slice,
+                              min(all, (my_share + 1) * slice), out_row) && ok;
           if (p.status != nullptr && threadIdx.x == 0 && my_share == 0) atomicOr(p.status, 16);
         }
         FF_TRACE(p, 35);
         if (!ok && p.status != nullptr) atomicOr(p.status, 2);
       }
+    }
+    if (threadIdx.x == 32 && counted_before == static_cast<uint32_t>(p.grid_ctas) - 1u) {
+      ctrl[kPushDoneWord] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) = push.step;
     }
   }
 }

@@ -23,6 +23,9 @@ STAGES = [
     (28, "merge_scan"), (29, "merge_fine_loads"), (30, "merge_threshold"), (2, "merge_end"),
     (3, "sweep2_collect"), (4, "gather_to_peers"), (20, "final_barrier"), (22, "finish_bin_hist"),
     (23, "finish_scan"), (24, "finish_scatter"), (31, "finish_queue_units"), (25, "finish_rank_emit"),
+    # context-parallel single-kernel step only
+    (32, "select_done"), (36, "merge_start"), (33, "peer_heads_staged"), (37, "own_candidate_ranked"), (34, "heads_checked"),
+    (35, "merged_and_written"),
 ]
 
 CASES = {
@@ -75,17 +78,87 @@ def format_timeline(stamps, mhz):
             continue
         parts.append(f"{name} {(stamps[slot] - prev) / mhz:.2f}")
         prev = stamps[slot]
-    total = (stamps[25] - stamps[0]) / mhz
+    total = (max(stamps[25], stamps[35]) - stamps[0]) / mhz
     return f"total {total:.2f} us | " + " | ".join(parts)
+
+
+def trace_context_parallel(mhz: float, shard_columns: int = 1 << 20, k: int = 2048, hinted: bool = False):
+    """Under torch.distributed.run (one rank per GPU): a few context-parallel steps on bf16-rounded
+    N(0,1) shards, the last one traced.  Every rank reports, over its own CTAs (cycle counters of
+    different GPUs are not comparable), when the select was done, how long the merging CTAs then
+    waited for the peers' run heads, and how long checking, ranking and writing took."""
+    import os
+    import torch.distributed as dist
+    from . import new_threshold_hint
+    from .context_parallel import ContextParallelTopk
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    lib = _lib.load()
+    g = torch.Generator(device=dev)
+    g.manual_seed(77 + rank)
+    shards = torch.randn((8, shard_columns), generator=g, device=dev).to(torch.bfloat16).float()
+    lengths = torch.tensor([shard_columns * world], dtype=torch.int32, device=dev)
+    buf = torch.zeros((1024, _lib.TRACE_SLOTS), dtype=torch.int64, device=dev)
+    hint = new_threshold_hint(1, dev) if hinted else None
+    with ContextParallelTopk(1, k, dev) as plan:
+        for i in range(6):
+            plan(shards[i:i + 1], lengths, rank * shard_columns, threshold_hint=hint)
+        torch.cuda.synchronize()
+        dist.barrier()
+        # ten steps replayed from one CUDA graph, all traced into the same slots: what is read back is
+        # the LAST step, taken with the ranks in step with each other (an eager launch would
+        # mostly show how far apart the ranks' host threads are)
+        lib.ff_topk_set_trace_buffer(buf.data_ptr())
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(10):
+                    plan(shards[i % 8:i % 8 + 1], lengths, rank * shard_columns, threshold_hint=hint)
+            torch.cuda.synchronize()
+            dist.barrier()
+            graph.replay()
+        torch.cuda.synchronize()
+        lib.ff_topk_set_trace_buffer(None)
+        plan.check_status()
+        t = buf.cpu().numpy()
+        t = t[t[:, 0] != 0]
+        merging = t[t[:, 35] != 0]
+        # the cycle counter is per SM: only differences inside one CTA mean anything
+        dur = lambda a, b, rows: (rows[:, b] - rows[:, a]) / mhz
+        sel = dur(0, 32, t)
+        line = f"rank {rank}: ctas {t.shape[0]} merging {merging.shape[0]} | select (start to select_done) {sel.min():.2f}..{sel.max():.2f}"
+        if merging.shape[0]:
+            parts = [("wait+stage heads", 36, 33), ("rank own", 33, 37), ("verdict barrier", 37, 34), ("write", 34, 35),
+                     ("whole CTA", 0, 35)]
+            line += " | merging CTAs (min..max): " + ", ".join(
+                f"{n} {dur(a, b, merging).min():.2f}..{dur(a, b, merging).max():.2f}" for n, a, b in parts)
+        lines = [None] * world
+        dist.all_gather_object(lines, line)
+        if rank == 0:
+            print(f"== context-parallel step, {world} ranks x {shard_columns} columns, k={k}"
+                  f"{' (threshold guesses)' if hinted else ''}, exchange {plan.exchange} (us at {mhz} MHz)")
+            for l in lines:
+                print("  " + l)
+            print(f"  rank 0, first CTA: {format_timeline(t[0], mhz)}")
+    dist.destroy_process_group()
 
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--cp", action="store_true",
+                    help="trace one context-parallel step (run under torch.distributed.run, one rank per GPU)")
     ap.add_argument("--case", default="all", choices=["all"] + sorted(CASES))
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--mhz", type=float, default=1965.0, help="SM clock used to convert cycles to us")
     ap.add_argument("--hinted", action="store_true", help="trace a launch that uses a threshold guess")
     args = ap.parse_args()
+    if args.cp:
+        trace_context_parallel(args.mhz, hinted=args.hinted)
+        return
     dev = torch.device("cuda:0")
     mhz = args.mhz
     names = sorted(CASES) if args.case == "all" else [args.case]
