@@ -423,11 +423,32 @@ def bench_extras(dev, lib, peak):
         k_bytes = 128 * int(l0.sum())
         us_p = _time_calls(lambda i: indexer_logits_fp8(q, kc, w, l0, out=sc), 1, 20, dev)
         us_pt = _time_calls(lambda i: (indexer_logits_fp8(q, kc, w, l0, out=sc), fast_topk_v3(sc, l0, K_TOP, out=o)), 1, 20, dev)
+        # the decode-step form: guesses carried from step to step, and the producer handing the select
+        # its survivors (every score not below the guess is listed while the scores are written)
+        from flash_float_jit_kernels_b200.indexer_logits import indexer_topk, new_handover
+        hint = new_threshold_hint(B, dev)
+        us_hint = _time_calls(lambda i: indexer_topk(q, kc, w, l0, K_TOP, scores=sc, out=o, threshold_hint=hint), 1, 20, dev)
+        hint2 = new_threshold_hint(B, dev)
+        hand = new_handover(B, dev)
+        status.zero_()
+        step = lambda i: indexer_topk(q, kc, w, l0, K_TOP, scores=sc, out=o, threshold_hint=hint2, status=status,
+                                      handover=hand)
+        us_hand = _time_calls(step, 1, 20, dev)
+        status.zero_()
+        step(0)
+        missed = int(status.item())
+        o_plain = torch.empty_like(o)
+        fast_topk_v3(sc, l0, K_TOP, out=o_plain)
+        torch.cuda.synchronize()
+        assert torch.equal(o, o_plain), "bench: the hand-over step disagrees with the plain select"
         out["indexer_logits_b64_ragged"] = {
             "producer_us": round(us_p, 2), "k_cache_bytes_read": k_bytes,
             "achieved_gbs": round(k_bytes / (us_p * 1e-6) / 1e9, 1),
             "frac_of_measured_peak": round(k_bytes / (us_p * 1e-6) / 1e9 / peak, 4),
-            "producer_plus_topk_us": round(us_pt, 2)}
+            "producer_plus_topk_us": round(us_pt, 2),
+            "producer_plus_topk_threshold_hint_us": round(us_hint, 2),
+            "producer_plus_topk_hand_over_us": round(us_hand, 2),
+            "hand_over_status_after_steady_state_step": missed}
         del kc, sc
     except Exception as e:   # the producer is a separate library; its absence must not hide the top-k numbers
         out["indexer_logits_b64_ragged"] = {"error": str(e)[:200]}

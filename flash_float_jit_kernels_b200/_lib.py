@@ -21,6 +21,7 @@ SIGNATURES = {
     "ff_topk_set_cluster_override": (c_int, [c_int32]),
     "ff_topk_set_trace_buffer": (c_int, [c_void_p]),
     "ff_topk_set_groups_override": (c_int, [c_int32]),
+    "ff_topk_set_self_seed": (c_int, [c_int32]),
     "ff_topk_policy_cluster_size": (c_int32, [c_int32, c_int64, c_int32]),
     "ff_topk_policy_launch_shape": (c_int, [c_int32, c_int64, c_int32, c_int32, c_int32, ctypes.POINTER(c_int32)]),
     "ff_topk_workspace_bytes": (c_size_t, [c_int32, c_int64, c_int32]),
@@ -28,6 +29,11 @@ SIGNATURES = {
         c_int,
         [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32,
          c_void_p, c_size_t, c_void_p, c_void_p],
+    ),
+    "ff_topk_launch_handover": (
+        c_int,
+        [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int64, c_int32,
+         c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p],
     ),
     "ff_topk_launch_typed": (
         c_int,
@@ -96,10 +102,12 @@ FF_EPILOGUE_INDEX = 0
 FF_EPILOGUE_PAGE_TABLE = 1
 FF_EPILOGUE_ADD_OFFSET = 2
 FF_TOPK_MAX_K = 2048
+FF_TOPK_HANDOVER_ROW_BYTES = 64 + 4096 * 8
 FF_DTYPE_F32, FF_DTYPE_BF16, FF_DTYPE_F16 = 0, 1, 2
 FF_STATUS_WAIT_TIMEOUT = 2
 FF_STATUS_HINT_MISSED = 8
 FF_STATUS_CP_SECOND_ROUND = 16
+FF_STATUS_BOUNDS = 32
 TRACE_SLOTS = 40
 
 
@@ -122,6 +130,23 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
         except AttributeError as exc:
             raise LibraryMissingError(f"{path} does not export {name}") from exc
+        fn.restype = restype
+        fn.argtypes = argtypes
+    return lib
+
+
+@functools.lru_cache(maxsize=None)
+def load_checked() -> ctypes.CDLL:
+    """The bounds-checked build of the same library (``build.build_checked_library``), for debugging
+    and for the test that runs the golden vectors through it; same prototypes."""
+    from .build import checked_lib_path
+    path = checked_lib_path()
+    if not path.exists():
+        raise LibraryMissingError(f"{path} is missing: build it with "
+                                  "`python -m flash_float_jit_kernels_b200.build --checked`")
+    lib = ctypes.CDLL(str(path))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)
         fn.restype = restype
         fn.argtypes = argtypes
     return lib

@@ -78,6 +78,25 @@ def build_library(force: bool = False, verbose: bool = False, extra_flags=()) ->
     return _compile(out, SOURCES, verbose, extra_flags)
 
 
+CHECKED_LIB_NAME = "libff_topk_checked.so"   # the same library compiled with -DFF_BOUNDS_CHECK
+
+
+def checked_lib_path() -> Path:
+    return CSRC / CHECKED_LIB_NAME
+
+
+def build_checked_library(force: bool = False, verbose: bool = False) -> Path:
+    """``csrc/libff_topk_checked.so``: ``ff_topk.cu`` with ``-DFF_BOUNDS_CHECK``, in which every
+    data-dependent index into a work array is range-checked and a violation sets
+    ``FF_STATUS_BOUNDS`` in the status word instead of touching memory (a debugging build;
+    the product loads ``libff_topk.so``)."""
+    out = checked_lib_path()
+    deps = [CSRC / s for s in SOURCES + HEADERS] + [INCLUDE / "ff_topk.h"]
+    if not force and out.exists() and all(d.stat().st_mtime <= out.stat().st_mtime for d in deps if d.exists()):
+        return out
+    return _compile(out, SOURCES, verbose, ["-DFF_BOUNDS_CHECK"])
+
+
 def build_indexer_library(force: bool = False, verbose: bool = False, extra_flags=()) -> Path:
     """Compile ``csrc/ff_indexer_logits.cu`` into ``csrc/libff_indexer.so`` (sm_100a)."""
     out = indexer_lib_path()
@@ -121,3 +140,5 @@ if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
     print(build_indexer_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
     print(build_tvmffi_module(force="--force" in sys.argv))
+    if "--checked" in sys.argv:
+        print(build_checked_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -60,7 +60,35 @@ struct Params {
   int32_t L_width;
   int32_t tiles_per_cta;  // target share of a CTA, in 128-key tiles
   int32_t* status;
+  const float* hint;      // [B] threshold guesses or null: scores not below hint[b] also go to the hand-over list
+  unsigned char* handover;   // per row FF_HANDOVER_ROW_BYTES: {count, readers, pad, uint64 entries[4096]}
 };
+
+constexpr int kHandoverCap = 4096;       // entries per row (the select's survivor capacity)
+constexpr int kHandoverWarpBuf = 64;     // composites an epilogue warp collects before it reserves list slots
+
+// Order-preserving fp32 -> uint32 map, the same as the select's (-0.0 == +0.0, NaN on top).
+__device__ __forceinline__ uint32_t monotone_key(float x) {
+  uint32_t u = __float_as_uint(x);
+  const uint32_t a = u & 0x7fffffffu;
+  if (a == 0u) u = 0u;
+  uint32_t k = u ^ (static_cast<uint32_t>(static_cast<int32_t>(u) >> 31) | 0x80000000u);
+  if (a > 0x7f800000u) k = 0xffffffffu;
+  return k;
+}
+
+// An epilogue warp moves its collected composites into the row's hand-over list: one global atomic
+// reserves the slots (so the round trip is paid once per about 32 survivors, not per tile), two
+// stores per lane fill them; what does not fit the list is dropped (the count tells the select).
+__device__ __forceinline__ void flush_handover(unsigned char* row_base, const unsigned long long* buf, int n, int lane) {
+  if (n == 0) return;
+  uint32_t base = 0;
+  if (lane == 0) base = atomicAdd(reinterpret_cast<uint32_t*>(row_base), static_cast<uint32_t>(n));
+  base = __shfl_sync(0xffffffffu, base, 0);
+  unsigned long long* list = reinterpret_cast<unsigned long long*>(row_base + 64);
+  for (int i = lane; i < n; i += 32)
+    if (base + i < static_cast<uint32_t>(kHandoverCap)) list[base + i] = buf[i];
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -192,6 +220,7 @@ struct Shared {
   uint32_t tmem_base;
   int timed_out;
   float w[kHeads];
+  unsigned long long handover[kEpilogueWarps][kHandoverWarpBuf];   // per epilogue warp: survivors not yet in the list
 };
 
 __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Params p) {
@@ -295,6 +324,13 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Param
     // ---------------- epilogue: thread = key (tensor memory lane) ----------------
     const int key_in_tile = warp * 32 + lane;
     float* out_row = p.scores + static_cast<int64_t>(row) * p.score_stride;
+    // hand-over to the select: scores not below the row's threshold guess are collected per warp
+    float hint = __uint_as_float(0x7fffffffu);   // NaN: no guess, nothing is handed over
+    if (p.hint != nullptr && p.handover != nullptr) hint = p.hint[row];
+    const bool hand_over = hint == hint;
+    unsigned char* row_base = p.handover + static_cast<int64_t>(row) * FF_HANDOVER_ROW_BYTES;
+    unsigned long long* mine = sh.handover[warp];
+    int n_mine = 0;   // uniform over the warp
     for (int i = 0; i < my_tiles; ++i) {
       const int buf = i & 1;
       (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((i / 2) & 1), &sh.timed_out);
@@ -305,6 +341,26 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Param
       mbar_arrive(smem_u32(&sh.tempty[buf]));
       const int key = (cta + i * n_ctas) * kTileKeys + key_in_tile;
       if (key < p.L_width) out_row[key] = key < len ? s : __uint_as_float(0xff800000u);
+      if (hand_over) {
+        const bool hit = key < len && !(s < hint);
+        const uint32_t votes = __ballot_sync(0xffffffffu, hit);
+        if (votes != 0u) {
+          if (hit)
+            mine[n_mine + __popc(votes & ((1u << lane) - 1u))] =
+                (static_cast<unsigned long long>(monotone_key(s)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(key));
+          n_mine += __popc(votes);
+          if (n_mine > kHandoverWarpBuf - 32) {   // the next tile might not fit: reserve list slots now
+            __syncwarp();
+            flush_handover(row_base, mine, n_mine, lane);
+            __syncwarp();
+            n_mine = 0;
+          }
+        }
+      }
+    }
+    if (hand_over) {
+      __syncwarp();
+      flush_handover(row_base, mine, n_mine, lane);
     }
   }
   tc_fence_before();
@@ -608,7 +664,18 @@ int64_t ff_indexer_launch_count(void) { return g_launches.load(); }
 int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_row_stride_bytes, const float* w,
                              const int32_t* lengths, float* scores, int64_t score_stride, int32_t B,
                              int32_t L_width, int32_t ctas_per_row, int32_t* status, void* stream) {
+  return ff_indexer_logits_launch_handover(q_e4m3, k_e4m3, k_row_stride_bytes, w, lengths, scores, score_stride, B,
+                                           L_width, ctas_per_row, nullptr, nullptr, status, stream);
+}
+
+int ff_indexer_logits_launch_handover(const void* q_e4m3, const void* k_e4m3, int64_t k_row_stride_bytes,
+                                      const float* w, const int32_t* lengths, float* scores, int64_t score_stride,
+                                      int32_t B, int32_t L_width, int32_t ctas_per_row, const float* hint,
+                                      void* handover, int32_t* status, void* stream) {
   if (B < 0 || L_width < 0) return fail(-2, "negative B or L_width");
+  if ((hint == nullptr) != (handover == nullptr)) return fail(-3, "hint and handover go together");
+  if (handover != nullptr && ((reinterpret_cast<uintptr_t>(handover) & 63u) != 0 || ctas_per_row < 0))
+    return fail(-2, "the hand-over list must be 64-byte aligned and needs the default kernel (ctas_per_row >= 0)");
   if (B == 0 || L_width == 0) return 0;
   if (q_e4m3 == nullptr || k_e4m3 == nullptr || w == nullptr || lengths == nullptr || scores == nullptr)
     return fail(-3, "q, k, w, lengths and scores must not be NULL");
@@ -636,6 +703,8 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
   p.L_width = L_width;
   p.tiles_per_cta = 0;
   p.status = status;
+  p.hint = hint;
+  p.handover = static_cast<unsigned char*>(handover);
   if (ctas_per_row < 0) {
     // The persistent kernel, two CTAs per SM, units of 8 tiles dealt out round robin.  Measured a few
     // per cent slower than shares of 32 tiles per CTA (below), which is therefore the default.

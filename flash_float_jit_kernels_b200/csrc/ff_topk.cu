@@ -19,6 +19,15 @@ std::atomic<int> g_cluster_override{0};
 std::atomic<int> g_groups_override{0};
 std::atomic<unsigned long long*> g_trace{nullptr};
 
+std::atomic<int> g_self_seed{-1};   // -1: FF_TOPK_SELF_SEED or on; 0 / 1: set through ff_topk_set_self_seed
+
+bool self_seed_enabled() {
+  const int v = g_self_seed.load(std::memory_order_relaxed);
+  if (v >= 0) return v != 0;
+  const char* env = getenv("FF_TOPK_SELF_SEED");
+  return env == nullptr || atoi(env) != 0;
+}
+
 constexpr int kMaxDevices = 64;
 std::once_flag g_init_once[kMaxDevices];
 int g_init_rc[kMaxDevices];
@@ -218,7 +227,10 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream, int dtype 
 
   // one instantiation per mode: the plain select carries no code of the others
   cudaError_t e;
-  const bool hints = q.hint_in != nullptr || q.hint_out != nullptr;
+  // A row split over clusters that has no guess makes its own (FF_TOPK_SELF_SEED=0 or
+  // ff_topk_set_self_seed(0) switch that off); the code lives in the instantiation with guesses.
+  if (!HAS_MAP && groups > 1 && self_seed_enabled()) q.self_seed = 1;
+  const bool hints = q.hint_in != nullptr || q.hint_out != nullptr || q.self_seed != 0;
   if (!HAS_MAP && dtype == FF_DTYPE_BF16)
     e = hints ? cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted, __nv_bfloat16>, q)
               : cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePlain, __nv_bfloat16>, q);
@@ -336,6 +348,11 @@ size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
   return static_cast<size_t>(B) * ff::kWsRowWords * sizeof(uint32_t);
 }
 
+int ff_topk_set_self_seed(int32_t on) {
+  g_self_seed.store(on < 0 ? -1 : (on != 0 ? 1 : 0));
+  return 0;
+}
+
 int ff_topk_set_groups_override(int32_t g) {
   if (g < 0 || g > 64) return fail(FF_ERR_BAD_CLUSTER, "groups override must be in [0, 64]");
   g_groups_override.store(g);
@@ -352,7 +369,7 @@ int transform_launch_impl(const void* scores_any, int dtype, int64_t row_stride,
                           int64_t table_stride, const int32_t* cu_seqlens_q,
                           int32_t n_table_rows, const int32_t* offsets, const float* hint_in,
                           float* hint_out, void* workspace, size_t workspace_bytes, int32_t* status,
-                          void* stream) {
+                          void* stream, void* handover = nullptr) {
   int rc = check_common(B, L_width, k);
   if (rc != 0) return rc;
   if (B == 0) return 0;
@@ -397,6 +414,13 @@ int transform_launch_impl(const void* scores_any, int dtype, int64_t row_stride,
   p.status = status;
   p.hint_in = hint_in;
   p.hint_out = hint_out;
+  if (handover != nullptr) {
+    if (hint_in == nullptr) return fail(FF_ERR_NULL, "a hand-over list needs the guesses it was built with (hint_in)");
+    if ((reinterpret_cast<uintptr_t>(handover) & 63u) != 0) return fail(FF_ERR_BAD_SHAPE, "handover must be 64-byte aligned");
+    if (dtype != FF_DTYPE_F32) return fail(FF_ERR_BAD_SHAPE, "the hand-over lists hold fp32 scores");
+    static_assert(FF_TOPK_HANDOVER_ROW_BYTES == ff::kHandoverRowBytes, "hand-over layout");
+    p.handover = static_cast<unsigned char*>(handover);
+  }
   int cluster = choose_cluster(device, B, L_width, k);
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0) {
     p.groups = choose_groups(device, B, L_width, workspace_bytes, &cluster, hint_in != nullptr);
@@ -436,6 +460,16 @@ int ff_topk_launch_hinted(const float* scores, int64_t row_stride, const int32_t
   return transform_launch_impl(scores, FF_DTYPE_F32, row_stride, lengths, row_starts, out_idx, 32, B, L_width, k,
                                FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, hint_in, hint_out, workspace,
                                workspace_bytes, status, stream);
+}
+
+int ff_topk_launch_handover(const float* scores, int64_t row_stride, const int32_t* lengths,
+                            const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width, int32_t k,
+                            const float* hint_in, float* hint_out, void* handover, void* workspace,
+                            size_t workspace_bytes, int32_t* status, void* stream) {
+  if (handover == nullptr) return fail(FF_ERR_NULL, "handover must not be NULL");
+  return transform_launch_impl(scores, FF_DTYPE_F32, row_stride, lengths, row_starts, out_idx, 32, B, L_width, k,
+                               FF_EPILOGUE_INDEX, nullptr, 0, nullptr, 0, nullptr, hint_in, hint_out, workspace,
+                               workspace_bytes, status, stream, handover);
 }
 
 int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengths,

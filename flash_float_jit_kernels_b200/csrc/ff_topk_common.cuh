@@ -118,6 +118,9 @@ struct TopkParams {
   int32_t* status;             // optional soft-error word
   const float* hint_in;        // [B] or null: a guess of a value between each row's k-th and 4096-th largest (NaN: none)
   float* hint_out;             // [B] or null: receives such a value for this call's rows (may alias hint_in)
+  unsigned char* handover;     // or null: per row kHandoverRowBytes {count, readers, pad to 64 B, uint64 entries[kSortCap]}:
+                               // the producer of the scores has already listed every score not below hint_in[row]
+  int32_t self_seed;           // 1: a row split over clusters that has no guess makes its own (see seed_own_guess)
   int32_t groups;              // clusters per row (> 1 needs workspace and a cooperative launch)
   uint32_t* workspace;         // zero-filled global scratch, kWsRowWords words per row
   PeerPtrs push_peers;         // context-parallel send: results go to these exchange buffers
@@ -134,6 +137,7 @@ struct TopkParams {
 };
 
 constexpr int kTraceSlots = 40;
+constexpr int kHandoverRowBytes = 64 + kSortCap * 8;   // FF_TOPK_HANDOVER_ROW_BYTES
 
 // Stage stamp for the per-CTA timeline: SM cycle counter, thread 0 only.
 #define FF_TRACE(p, slot)                                                                 \
@@ -141,6 +145,23 @@ constexpr int kTraceSlots = 40;
     if ((p).trace != nullptr && threadIdx.x == 0)                                         \
       (p).trace[static_cast<size_t>(blockIdx.x) * ff::kTraceSlots + (slot)] = clock64();  \
   } while (0)
+
+// Bounds-checked build (-DFF_BOUNDS_CHECK): every data-dependent index into a shared or global
+// work array is tested first; an index outside its array sets FF_STATUS_BOUNDS (32) and the number
+// of the place in bits 8.. of the status word, and the access is skipped: nothing traps and the
+// kernel runs on to its end (its result is then not to be trusted).  It stands in for a memory
+// checker on machines where none can be run (the reference's counterpart is a static lint,
+// tools/kernel_lint.py:58-163).  In the normal build the test compiles to nothing.
+#ifdef FF_BOUNDS_CHECK
+__device__ __forceinline__ bool index_in_range(int32_t* status, long long idx, long long n, int place) {
+  if (idx >= 0 && idx < n) return true;
+  if (status != nullptr) atomicOr(status, 32 | (place << 8));
+  return false;
+}
+#define FF_IN_RANGE(p, idx, n, place) ff::index_in_range((p).status, static_cast<long long>(idx), static_cast<long long>(n), (place))
+#else
+#define FF_IN_RANGE(p, idx, n, place) true
+#endif
 
 // Exclusive suffix sum over the CTA: returns the sum of `v` over all threads
 // with a higher thread index; `total` receives the CTA-wide sum.

@@ -542,11 +542,16 @@ __device__ __forceinline__ void scan_tile(uint32_t tile, int units, int first_un
 //   [320 + 6 * 8192, + 2 * 4096) survivor list (4096 x 64-bit composites), then a second one for a hinted
 //                                attempt.  Both are zero between launches: an entry is valid once it is
 //                                non-zero (no composite is zero), so readers need no barrier after the writes
+//   then 64 words                a row that seeds its own threshold guess: one 64-bit accumulator of the
+//                                CTAs' estimates (sum of keys, CTAs with an estimate, CTAs reported)
 constexpr int kWsCoarseWord = 64;            // 256 coarse bins (sums of 32 first-level bins) of the row
 constexpr int kWsHeaderWords = 64 + 256;
 constexpr int kWsHistWords = kNumLevels * kMaxBins;
 constexpr int kWsListWords = 2 * kSortCap;     // one survivor list (64-bit composites)
-constexpr int kWsRowWords = kWsHeaderWords + kWsHistWords + 2 * kWsListWords;   // + the list of a hinted attempt
+constexpr int kWsSeedWord = kWsHeaderWords + kWsHistWords + 2 * kWsListWords;   // 64-bit accumulator of the CTAs' own threshold estimates
+constexpr int kWsSeedWords = 64;
+static_assert(kWsSeedWord % 2 == 0, "the accumulator is a 64-bit word");
+constexpr int kWsRowWords = kWsSeedWord + kWsSeedWords;
 constexpr int kSpinLimit = 1 << 21;   // bounded polling of a row barrier (about a second)
 
 // All `expected` CTAs of a row meet here (they are co-resident: cooperative
@@ -904,6 +909,160 @@ __device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C
   FF_TRACE(p, 30);
 }
 
+// ---- a row seeds its own threshold guess ----------------------------------------------------
+// A threshold guess (a score between the row's k-th and 4096-th largest) lets the row be selected in
+// one sweep without histogram, merge or second sweep.  When the caller has none and the row is
+// spread over many CTAs, the row makes one: every CTA estimates, from the first tile of its own
+// chunk, the score that about `target` scores of the whole row reach; the CTAs add their
+// estimates into one word of the row's global scratch, and all take the mean.  If the
+// guess does not fit, the row falls back to the histogram path like after any other guess, so
+// the result stays exact; only rows whose chunks look alike (no trend along the row) profit.
+//
+// The estimate of one CTA: each of its threads keeps the largest of the few scores it reads (g of
+// them); with p = target / length, a thread's largest reaches the wanted score v with probability
+// q = 1 - (1 - p)^g, so about rho = threads * q of them do, and the rho-th largest of the threads'
+// maxima estimates v.  The CTA's 32 largest maxima come out of a bitonic sort inside every warp
+// and four rounds of pairwise bitonic merges that keep the upper 32.
+struct SeedPlan {
+  bool use;        // uniform over all CTAs of the row
+  float p;         // target / length
+  int n_use;       // 16-byte units of a CTA's first tile that it looks at
+};
+// Row-level decision, from quantities every CTA of the row computes alike.
+__device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, int n_share, int k) {
+  SeedPlan sp;
+  sp.use = false;
+  const int target = min(k + (k >> 2) + 64, kSortCap - (kSortCap >> 3));   // hint_target_rank(k)
+  sp.p = static_cast<float>(target) / static_cast<float>(len);
+  if (n_share > kThreads || len < 4 * target) return sp;   // (the accumulator's counters hold up to 1023)
+  const int U = static_cast<int>((static_cast<int64_t>(len) + mis + per_unit - 1) / per_unit);
+  const int per = (U + n_share - 1) / n_share;          // units per CTA, as make_chunk cuts them
+  int n0 = min(per, kTileUnits);                        // units of a CTA's first tile
+  if (n0 < 64) return sp;
+  auto rho_of = [&](int units) {
+    const int lanes = min(kThreads, units);
+    const float g = static_cast<float>(per_unit) * static_cast<float>(units) / static_cast<float>(lanes);
+    return static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-sp.p)));
+  };
+  float rho = rho_of(n0);
+  if (rho > 26.f) {
+    // more hits than the kept 32 can show: look at a part of the tile only (a multiple of the
+    // thread count, so that every thread reads the same number of units)
+    n0 = max(kThreads, (static_cast<int>(static_cast<float>(n0) * 24.f / rho) / kThreads) * kThreads);
+    rho = rho_of(n0);
+  }
+  sp.n_use = n0;
+  // a usable order statistic inside the kept 32, and enough hits over the row for a steady mean
+  sp.use = rho >= 3.f && rho <= 30.f && rho * static_cast<float>(n_share) >= 600.f;
+  return sp;
+}
+
+struct SeedResult {
+  float guess;
+  int code;   // 1: a guess, 0: none, 2: none and a bounded wait ran out
+};
+// tile0: shared address of the chunk's first tile (landed), n0: its 16-byte units.
+template <typename T>
+__device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* flag, uint32_t* scratch, uint32_t* ws,
+                                                  float p_frac, int n_share, int my_share) {
+  constexpr int kPU = Elem<T>::kPerUnit;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int w = tid >> 5;
+  uint32_t* sorted = scratch + 32;       // [kWarps][32] (scratch[0]: the result, handed to all threads)
+  SeedResult res;
+  res.guess = 0.f;
+  res.code = 0;
+  // ---- largest score per thread over the first tile of the chunk ----
+  uint32_t mkey = 0u;
+  if (n0 > 0) {
+    float m = __uint_as_float(0xff800000u);
+    bool any = false;
+#pragma unroll
+    for (int j = 0; j < kTileUnits / kThreads; ++j) {
+      const int lu = tid + j * kThreads;
+      if (lu < n0) {
+        float v[kPU];
+        unpack_unit<T>(lds_u4(tile0 + 16u * static_cast<uint32_t>(lu)), v);
+#pragma unroll
+        for (int e = 0; e < kPU; ++e) m = fmaxf(m, v[e]);   // (NaN scores are left out of the estimate)
+        any = true;
+      }
+    }
+    if (any) mkey = key_of(m);
+  }
+  // ---- the CTA's 32 largest thread maxima, descending ----
+#pragma unroll
+  for (int k2 = 2; k2 <= 32; k2 <<= 1) {
+#pragma unroll
+    for (int j = k2 >> 1; j > 0; j >>= 1) {
+      const uint32_t o = __shfl_xor_sync(0xffffffffu, mkey, j);
+      const bool keep_max = ((lane & j) == 0) == ((lane & k2) == 0);
+      mkey = keep_max ? max(mkey, o) : min(mkey, o);
+    }
+  }
+  sorted[w * 32 + lane] = mkey;
+  __syncthreads();
+#pragma unroll 1
+  for (int stride = 1; stride < kWarps; stride <<= 1) {
+    if ((w & (2 * stride - 1)) == 0) {
+      // upper 32 of two descending lists: pair element i of one with element 31 - i of the other, keep
+      // the larger (a bitonic sequence), and sort it again with one bitonic merge
+      uint32_t v = max(mkey, sorted[(w + stride) * 32 + 31 - lane]);
+#pragma unroll
+      for (int j = 16; j > 0; j >>= 1) {
+        const uint32_t o = __shfl_xor_sync(0xffffffffu, v, j);
+        v = ((lane & j) == 0) ? max(v, o) : min(v, o);
+      }
+      mkey = v;
+      sorted[w * 32 + lane] = v;
+    }
+    __syncthreads();
+  }
+  // ---- this CTA's estimate: the rho-th largest thread maximum, added to the row's accumulator ----
+  // One 64-bit word per row collects all estimates: bits 0..43 the sum of the estimates' keys, bits
+  // 44..53 how many CTAs gave one, bits 54..63 how many CTAs have reported at all.  One atomic
+  // per CTA adds all three, so a reader sees them consistently, and one thread per CTA polls the
+  // single word until every CTA has reported (many threads polling many words cost several
+  // microseconds here: the pollers crowd out the writers in L2).
+  unsigned long long* acc = reinterpret_cast<unsigned long long*>(ws + kWsSeedWord);
+  if (tid == 0) {
+    unsigned long long add = 1ull << 54;
+    const int lanes = min(kThreads, n0);
+    if (lanes >= 32) {
+      const float g = static_cast<float>(kPU) * static_cast<float>(n0) / static_cast<float>(lanes);
+      const float rho = static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-p_frac)));
+      const int r = min(max(static_cast<int>(rho + 0.5f), 1), 32);
+      const uint32_t key = sorted[r - 1];
+      // (keys above +inf's are NaN patterns, key 0 means fewer than r threads had a score: no estimate)
+      if (key != 0u && key <= 0xff800000u) add |= (1ull << 44) | key;
+    }
+    atomicAdd(acc, add);
+    unsigned long long v = 0ull;
+    int spin = 0;
+    for (; spin < kSpinLimit; ++spin) {
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(acc) : "memory");
+      if (static_cast<int>(v >> 54) >= n_share) break;
+    }
+    const int valid = static_cast<int>((v >> 44) & 1023ull);
+    // the mean of the keys (keys are close to linear in the score over so narrow a range)
+    uint32_t mean = 0u;
+    if (spin < kSpinLimit && 2 * valid >= n_share) mean = static_cast<uint32_t>((v & ((1ull << 44) - 1ull)) / static_cast<unsigned long long>(valid));
+    *flag = spin < kSpinLimit ? 1 : 0;
+    scratch[0] = mean;
+  }
+  __syncthreads();
+  const uint32_t mean = scratch[0];
+  const bool ok = *flag != 0;
+  __syncthreads();
+  if (!ok) res.code = 2;
+  if (ok && mean != 0u) {
+    res.guess = __uint_as_float(bits_of_key(mean));
+    res.code = 1;
+  }
+  return res;
+}
+
 // How many scores the next call's guess should let through: between k (fewer is a miss) and
 // kSortCap (more is a miss), nearer to k because the finish costs grow with the square of it.
 __device__ __forceinline__ int hint_target_rank(int k) { return min(k + (k >> 2) + 64, kSortCap - (kSortCap >> 3)); }
@@ -945,6 +1104,7 @@ __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, i
   } else {
     o = is_map ? idx : static_cast<int32_t>(idx + p.shard_offset);
   }
+  if (!FF_IN_RANGE(p, j, p.k, 9) || !FF_IN_RANGE(p, row, p.B, 10)) return;
   if (p.out_idx64 != nullptr) p.out_idx64[static_cast<int64_t>(row) * p.k + j] = o;
   else p.out_idx[static_cast<int64_t>(row) * p.k + j] = o;
   if (p.out_val != nullptr) {
@@ -1026,6 +1186,12 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
   if (identity || len <= k) {
     if (my_share != 0) return;
+    if (kHinted && !HAS_MAP && p.handover != nullptr && tid == 0) {
+      // nobody reads this row's hand-over list in this launch: leave its header zeroed for the next producer
+      uint32_t* hdr = reinterpret_cast<uint32_t*>(p.handover + static_cast<int64_t>(row) * kHandoverRowBytes);
+      hdr[0] = 0u;
+      hdr[1] = 0u;
+    }
     if (kHinted && !HAS_MAP && p.hint_out != nullptr && tid == 0) p.hint_out[row] = __uint_as_float(0x7fffffffu);   // no guess
     if (!HAS_MAP && p.out_val != nullptr) {
       // Context-parallel shard shorter than k: every position is a candidate, but the
@@ -1160,6 +1326,65 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     use_hint = hint == hint;   // NaN: no guess
   }
   __syncthreads();
+  if (kHinted && !HAS_MAP && p.handover != nullptr) {
+    // Hand-over from the kernel that produced the scores: it has already listed every score of
+    // the row that is not below the guess (composites, in arrival order) and counted them.  If
+    // the count fits, every CTA of the row copies the list and goes straight to the finish: no
+    // score is read at all.  If it does not fit (or there was no guess), the count says so
+    // exactly, so the row skips the sweep with the guess and selects from the scores.
+    uint32_t* hdr = reinterpret_cast<uint32_t*>(p.handover + static_cast<int64_t>(row) * kHandoverRowBytes);
+    uint32_t readers_before = 0u;
+    if (tid == 0) {
+      sh.push_base = static_cast<int>(__ldcg(hdr));
+      __threadfence();                               // the count is read before this CTA counts itself as a reader
+      readers_before = atomicAdd(hdr + 1, 1u);       // (looked at below, after the copy: its round trip overlaps)
+    }
+    __syncthreads();
+    const int listed = sh.push_base;
+    if (use_hint && listed >= k && listed <= kSortCap) {
+      const unsigned long long* list = reinterpret_cast<const unsigned long long*>(hdr + 16);
+      for (int i = tid; i < listed; i += kThreads) sortbuf[i] = __ldcg(list + i);
+      hinted_done = true;
+      expected_total = listed;
+      floor_comp = static_cast<uint64_t>(key_of(hint)) << 32;
+      if (my_share == 0 && tid == 0) sh.sort_count = listed;
+    } else if (use_hint) {
+      if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 8);
+    }
+    use_hint = false;
+    // the reader that counts itself last leaves the header zeroed for the next producer launch
+    if (tid == 0 && readers_before == static_cast<uint32_t>(n_share) - 1u) {
+      hdr[0] = 0u;
+      hdr[1] = 0u;
+    }
+    __syncthreads();
+  }
+  bool self_seeded = false;
+  if (kHinted && !HAS_MAP && p.self_seed != 0 && G > 1 && !use_hint && !hinted_done && p.handover == nullptr) {
+    const SeedPlan sp = seed_plan(len, chunk.mis, kPU, n_share, k);
+    if (sp.use) {
+      // the chunk's first tile (it stays in the ring for the sweep that follows)
+      const int n0 = ts.n_tiles > 0 ? tile_units(ts, 0) : 0;
+      if (n0 > 0) {
+        if (ts.held0 != 0) {
+          __syncthreads();
+          stream_fetch(ts, 0);
+        }
+        if (!ts.arrived0) {
+          if (!mbar_wait(ts.bars, static_cast<uint32_t>(ts.fidx0 & 1))) ts.timed_out = true;
+          ts.arrived0 = true;
+        }
+      }
+      const SeedResult sr = seed_own_guess<T>(ts.ring, min(n0, sp.n_use), &sh.flag, hist, ws, sp.p, n_share, my_share);
+      if (sr.code == 2) ts.timed_out = true;
+      if (sr.code == 1) {
+        hint = sr.guess;
+        use_hint = true;
+        self_seeded = true;
+      }
+      FF_TRACE(p, 21);
+    }
+  }
   if (kHinted && use_hint) {
     stream_pass(ts, [&](uint32_t tile, int tt, int units) {
       collect_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, hint, stage, kSortCap, &sh.stage_count);
@@ -1209,7 +1434,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         if (my_share == 0 && tid == 0) sh.sort_count = total;
       }
     } else {
-      if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 8);
+      // a caller's guess that did not fit is reported; the row's own guess is its own business
+      if (!self_seeded && p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 8);
       if (C > 1 && G == 1) cluster.sync();   // every CTA has read the count before it is cleared
       if (tid == 0) sh.sort_count = 0;
     }
@@ -1234,12 +1460,15 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
           float v[kPU];
           unpack_unit<T>(lds_u4(tile + 16u * static_cast<uint32_t>(lu)), v);
 #pragma unroll
-          for (int e = 0; e < kPU; ++e) atomicAdd(&hist[raw_digit(v[e])], 1u);
+          for (int e = 0; e < kPU; ++e) {
+            const uint32_t d = raw_digit(v[e]);
+            if (FF_IN_RANGE(p, d, kMaxBins, 1)) atomicAdd(&hist[d], 1u);
+          }
         }
       }
     });
     float x = 0.f;
-    if (partial_element(chunk, x) >= 0) atomicAdd(&hist[raw_digit(x)], 1u);
+    if (partial_element(chunk, x) >= 0 && FF_IN_RANGE(p, raw_digit(x), kMaxBins, 2)) atomicAdd(&hist[raw_digit(x)], 1u);
   }
   __syncthreads();
   FF_TRACE(p, 1);
@@ -1404,6 +1633,9 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       const int n_plain = hinted_done ? 0 : (ok ? n_load : kSortCap);
       for (int i = tid; i < 2 * n_plain; i += kThreads) lists[i] = 0u;
       for (int i = tid; i < 2 * hinted_total; i += kThreads) lists[kWsListWords + i] = 0u;
+      if (kHinted && p.self_seed != 0) {
+        if (tid < 2) ws[kWsSeedWord + tid] = 0u;
+      }
     }
   } else if (C > 1) {
     if (!hinted_done) cluster.sync();   // every survivor has landed in every CTA's list
@@ -1561,7 +1793,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
     const uint32_t b = static_cast<uint32_t>((sortbuf[i] - lo) >> bshift);
-    at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
+    if (FF_IN_RANGE(p, b, kFinishBins, 3)) at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
   }
   __syncthreads();
   FF_TRACE(p, 22);
@@ -1587,7 +1819,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const uint32_t at = E[b] + at_arr[i];
     at_arr[i] = static_cast<uint16_t>(at);
-    bucketed[at] = c;
+    if (FF_IN_RANGE(p, at, kSortCap, 4)) bucketed[at] = c;
   }
   __syncthreads();
   FF_TRACE(p, 24);
@@ -1608,9 +1840,11 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (n_b <= kUnitBucket) {
       const int nu = static_cast<int>((n_b + 15u) >> 4);
       const int base = atomicAdd(&sh.small_count, nu);
-      for (int u = 0; u < nu; ++u) units[base + u] = (static_cast<uint32_t>(at_arr[i]) << 8) | static_cast<uint32_t>(u);
+      for (int u = 0; u < nu; ++u)
+        if (FF_IN_RANGE(p, base + u, 2 * kSortCap, 5)) units[base + u] = (static_cast<uint32_t>(at_arr[i]) << 8) | static_cast<uint32_t>(u);
     } else {
-      big_list[atomicAdd(&sh.big_count, 1)] = at_arr[i];
+      const int slot = atomicAdd(&sh.big_count, 1);
+      if (FF_IN_RANGE(p, slot, kSortCap, 6)) big_list[slot] = at_arr[i];
     }
   }
   __syncthreads();
@@ -1632,7 +1866,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         const uint64_t o = bucketed[q];
         cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
       }
-      if (cnt != 0u) atomicAdd(&rankcnt[me], cnt);
+      if (cnt != 0u && FF_IN_RANGE(p, me, kSortCap, 7)) atomicAdd(&rankcnt[me], cnt);
     }
     const int n_big = sh.big_count;
     const int lane = tid & 31;
@@ -1650,7 +1884,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
         cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
       }
       cnt = __reduce_add_sync(0xffffffffu, cnt);
-      if (lane == 0) rankcnt[me] = cnt;
+      if (lane == 0 && FF_IN_RANGE(p, me, kSortCap, 8)) rankcnt[me] = cnt;
     }
   }
   __syncthreads();

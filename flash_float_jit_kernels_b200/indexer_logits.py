@@ -29,6 +29,11 @@ SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32,
          c_void_p, c_void_p],
     ),
+    "ff_indexer_logits_launch_handover": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32,
+         c_void_p, c_void_p, c_void_p, c_void_p],
+    ),
     "ff_indexer_launch_count": (c_int64, []),
     "ff_indexer_last_error_string": (c_char_p, []),
 }
@@ -48,10 +53,32 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+def new_handover(B: int, device) -> torch.Tensor:
+    """A zero-filled survivor hand-over buffer for ``B`` rows (see :func:`indexer_topk`)."""
+    from . import _lib
+    return torch.zeros(B * _lib.FF_TOPK_HANDOVER_ROW_BYTES, dtype=torch.uint8, device=device)
+
+
+def _check_handover(handover, threshold_hint, B, device):
+    from . import _lib
+    _require(threshold_hint is not None, "a hand-over buffer needs threshold_hint (the guesses the lists are built with)")
+    _require(handover.dtype == torch.uint8 and handover.is_contiguous() and handover.device == device
+             and handover.numel() >= B * _lib.FF_TOPK_HANDOVER_ROW_BYTES,
+             "handover must be a contiguous uint8 tensor from new_handover(B, device)")
+    _require(threshold_hint.shape == (B,) and threshold_hint.dtype == torch.float32 and threshold_hint.is_contiguous()
+             and threshold_hint.device == device, "threshold_hint must be a contiguous (B) float32 tensor")
+
+
 def indexer_logits_fp8(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, lengths: torch.Tensor, *,
                        out: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-                       ctas_per_row: int = 0) -> torch.Tensor:
+                       ctas_per_row: int = 0, threshold_hint: Optional[torch.Tensor] = None,
+                       handover: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Scores of every key of every row.
+
+    With ``handover`` (from :func:`new_handover`) and ``threshold_hint`` the kernel also lists, per
+    row, every score not below the row's guess for the select that follows
+    (``fast_topk_v3(..., threshold_hint=..., handover=...)``), which then reads no score at all
+    when the guess fits.
 
     Args:
         q: (B, 64, 128) ``float8_e4m3fn`` (or uint8 holding those bytes), contiguous.
@@ -82,11 +109,14 @@ def indexer_logits_fp8(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, length
     if B == 0 or L == 0:
         return out
     lib = load()
+    if handover is not None:
+        _check_handover(handover, threshold_hint, B, q.device)
     with torch.cuda.device(q.device):
-        rc = lib.ff_indexer_logits_launch(
+        rc = lib.ff_indexer_logits_launch_handover(
             q.data_ptr(), k.data_ptr(), k.stride(0) if B > 1 else max(k.stride(0), L * HEAD_DIM), w.data_ptr(),
             lengths.data_ptr(), out.data_ptr(), out.stride(0) if B > 1 else max(out.stride(0), L), B, L,
-            int(ctas_per_row), _ptr(status), _stream_ptr(q.device))
+            int(ctas_per_row), None if handover is None else threshold_hint.data_ptr(), _ptr(handover),
+            _ptr(status), _stream_ptr(q.device))
     if rc < 0:
         raise TopkArgumentError(f"indexer_logits_fp8: {lib.ff_indexer_last_error_string().decode()}")
     if rc > 0:
@@ -96,14 +126,19 @@ def indexer_logits_fp8(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, length
 
 def indexer_topk(q: torch.Tensor, k: torch.Tensor, w: torch.Tensor, lengths: torch.Tensor, topk: int, *,
                  scores: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                 threshold_hint: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 threshold_hint: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
+                 handover: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One decode step of the indexer: logits from the fp8 K cache, then their top-k.
 
     Two launches on the current stream (producer, select), no host synchronisation; pass
     ``scores`` (B, L) float32, ``out`` (B, topk) int32 and, to carry threshold guesses from
     step to step, ``threshold_hint`` (see ``fast_topk_v3``) to keep the step allocation-free.
-    Returns the (B, topk) int32 indices.
+    With ``handover`` (:func:`new_handover`, kept from step to step like the guesses) the producer
+    hands the select its survivors: every score not below a row's guess is listed while the scores
+    are written, and a row whose guess fits is ranked from that list without reading a score.
+    Returns the (B, topk) int32 indices; the result is exact with or without guesses and lists.
     """
     from .topk_indexer import fast_topk_v3
-    scores = indexer_logits_fp8(q, k, w, lengths, out=scores, status=status)
-    return fast_topk_v3(scores, lengths, topk, out=out, status=status, threshold_hint=threshold_hint)
+    scores = indexer_logits_fp8(q, k, w, lengths, out=scores, status=status,
+                                threshold_hint=threshold_hint if handover is not None else None, handover=handover)
+    return fast_topk_v3(scores, lengths, topk, out=out, status=status, threshold_hint=threshold_hint, handover=handover)

@@ -93,6 +93,7 @@ def fast_topk_v3(
     status: Optional[torch.Tensor] = None,
     threshold_hint: Optional[torch.Tensor] = None,
     index_dtype: torch.dtype = torch.int32,
+    handover: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Top-k indices of every row of ``score`` (reference: ``topk_indexer.py:109``).
 
@@ -121,6 +122,11 @@ def fast_topk_v3(
             score of rank about 1.25 k of this call's row: pass the tensor again
             for the next call on similar rows (the next decode step).
 
+        handover: optional survivor lists written by the kernel that produced ``score`` with the
+            same ``threshold_hint`` (``indexer_logits.indexer_logits_fp8(..., handover=...)``):
+            a row whose guess fits is ranked from its list and no score is read; fp32 scores
+            and int32 indices only.
+
     Returns:
         (B, topk) int32 indices in (value desc, index asc) order, ``-1``
         padded for rows shorter than ``topk``.
@@ -146,7 +152,18 @@ def fast_topk_v3(
                  and threshold_hint.is_contiguous() and threshold_hint.device == dev,
                  "threshold_hint must be a contiguous (B) float32 tensor on score's device")
 
+    if handover is not None:
+        _require(not typed and threshold_hint is not None, "handover needs fp32 scores, int32 indices and threshold_hint")
+        _require(handover.dtype == torch.uint8 and handover.is_contiguous() and handover.device == dev
+                 and handover.numel() >= B * _lib.FF_TOPK_HANDOVER_ROW_BYTES,
+                 "handover must be a contiguous uint8 tensor of B * FF_TOPK_HANDOVER_ROW_BYTES bytes")
+
     def call():
+        if handover is not None:
+            return lib.ff_topk_launch_handover(
+                score.data_ptr(), row_stride, lengths.data_ptr(), _ptr(row_starts), out.data_ptr(), B, L, topk,
+                threshold_hint.data_ptr(), threshold_hint.data_ptr(), handover.data_ptr(), _ptr(ws), ws_bytes,
+                _ptr(status), stream)
         if typed:
             hint_ptr = None if threshold_hint is None else threshold_hint.data_ptr()
             return lib.ff_topk_launch_typed(

@@ -42,6 +42,22 @@ int ff_indexer_logits_launch(const void* q_e4m3, const void* k_e4m3, int64_t k_r
                              int64_t score_stride, int32_t B, int32_t L_width, int32_t ctas_per_row,
                              int32_t* status, void* stream);
 
+/* The same launch, which also hands the top-k select its survivors (no reference counterpart).
+ * hint: [B] float32 threshold guesses as ff_topk_launch_hinted carries them from step to step
+ * (NaN = no guess for that row).  Every score of row b that is not below hint[b] is, besides being
+ * written to `scores`, appended as a 64-bit composite (monotone key << 32 | ~index) to row b's
+ * hand-over list: handover + b * FF_HANDOVER_ROW_BYTES holds {uint32 count, uint32 readers, pad to
+ * 64 bytes, uint64 entries[4096]}; the count keeps counting past 4096, entries beyond are dropped.
+ * The counts must be zero when the launch starts (the buffer is zero-filled once by the caller;
+ * ff_topk_launch_handover leaves every count it has read at zero again).  With the list the select
+ * reads no score at all when the guess fits; when it does not, it falls back to the scores.
+ * Only the default kernel (ctas_per_row >= 0) takes a hand-over. */
+#define FF_HANDOVER_ROW_BYTES (64 + 4096 * 8)
+int ff_indexer_logits_launch_handover(const void* q_e4m3, const void* k_e4m3, int64_t k_row_stride_bytes,
+                                      const float* w, const int32_t* lengths, float* scores,
+                                      int64_t score_stride, int32_t B, int32_t L_width, int32_t ctas_per_row,
+                                      const float* hint, void* handover, int32_t* status, void* stream);
+
 int64_t ff_indexer_launch_count(void);
 const char* ff_indexer_last_error_string(void);
 

@@ -47,6 +47,9 @@ extern "C" {
 #define FF_STATUS_CP_SECOND_ROUND 16 /* information, not an error: a context-parallel step needed the ranks' whole
                                         candidate runs, not only their first part (winners crowded into few shards) */
 
+#define FF_STATUS_BOUNDS 32 /* only in the build with -DFF_BOUNDS_CHECK: an index fell outside its work array (the access
+                               was skipped; bits 8.. name the place); the result of that launch is not to be trusted */
+
 /* Output epilogue applied to each selected window-relative index `p`
  * (reference: topk_indexer_radix.cu:1000-1124, the fused page-table
  * transforms). */
@@ -93,7 +96,7 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
  * still works but handles a long row with a single cluster; this entry point
  * keeps the fast path (a long row split over several clusters) by using scratch
  * built into the library: a zero-initialised __device__ array of
- * FF_TOPK_STATIC_MAX_ROWS * 263,424 bytes (about 1029 KiB) that every GPU
+ * FF_TOPK_STATIC_MAX_ROWS * 263,680 bytes (about 1030 KiB) that every GPU
  * loading the library holds until the process exits.
  *   - B > FF_TOPK_STATIC_MAX_ROWS is rejected with FF_ERR_TOO_LARGE.
  *   - It calls no cudaMalloc / cudaFree and no allocating library routine; it
@@ -110,6 +113,22 @@ int ff_topk_launch(const float* scores, int64_t row_stride, const int32_t* lengt
 int ff_topk_launch_static(const float* scores, int64_t row_stride, const int32_t* lengths,
                           const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width,
                           int32_t k, int32_t* status, void* stream);
+
+/* ff_topk_launch_hinted for scores whose producer has already listed the survivors (no reference
+ * counterpart; the "producer fused with the first pass" step, whose shape the reference's README
+ * names, README.md:28).  `handover` is the buffer ff_indexer_logits_launch_handover
+ * (include/ff_indexer_logits.h) filled in the launch before this one on the same stream, with the
+ * guesses hint_in: per row FF_TOPK_HANDOVER_ROW_BYTES holding {uint32 count, uint32 readers, pad to
+ * 64 bytes, uint64 composites[4096]} of every score not below hint_in[row].  A row whose count is
+ * between k and 4096 is ranked from its list alone: no score is read.  Any other row (no guess, or a
+ * guess that let through too few or too many: FF_STATUS_HINT_MISSED) is selected from `scores` as
+ * by ff_topk_launch; the result is exact either way.  Every header that was read is left zeroed for
+ * the producer's next launch; hint_out receives the next guesses (may alias hint_in). */
+#define FF_TOPK_HANDOVER_ROW_BYTES (64 + 4096 * 8)
+int ff_topk_launch_handover(const float* scores, int64_t row_stride, const int32_t* lengths,
+                            const int32_t* row_starts, int32_t* out_idx, int32_t B, int64_t L_width, int32_t k,
+                            const float* hint_in, float* hint_out, void* handover, void* workspace,
+                            size_t workspace_bytes, int32_t* status, void* stream);
 
 /* ff_topk_launch for other score and index types (no reference counterpart: the reference is fp32
  * with int32 indices only and leaves a half-precision value type commented out,
@@ -261,6 +280,15 @@ int ff_topk_set_trace_buffer(void* device_buffer);
  * 2..64 = split every row with enough workspace over that many clusters of the
  * current cluster size, clamped to what can be co-resident).  Process-wide. */
 int ff_topk_set_groups_override(int32_t groups);
+
+/* Rows that are split over several clusters and come without a threshold guess make their own
+ * (every CTA estimates, from its own chunk, a score that about 1.25 k of the row's scores reach;
+ * the median of the estimates is tried like a caller's guess, with the same fall-back, so results
+ * are exact either way).  It pays on rows whose parts look alike and costs a few microseconds on
+ * rows with a strong trend along the row.  on = 0 switches it off, 1 on, -1 back to the default
+ * (on, unless the environment holds FF_TOPK_SELF_SEED=0).  Process-wide.  No reference counterpart
+ * (the reference finds its threshold from histograms only, topk_indexer_radix.cu:637-672). */
+int ff_topk_set_self_seed(int32_t on);
 
 /* The cluster size the automatic policy picks for (B, L_width, k) on the
  * current device (after overrides) when a row stays inside ONE cluster (no

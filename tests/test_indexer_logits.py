@@ -115,3 +115,52 @@ def test_decode_step_with_threshold_guesses(oracle):
             n = int(lengths[b])
             exp_scores[b, :n] = oracle.indexer_logits(q[b].float().numpy(), k[b, :n].float().numpy(), w[b].numpy())[0]
         assert np.array_equal(out.cpu().numpy(), oracle.topk_c(exp_scores, lengths.numpy(), k_top)), step
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,L,k_top", [(3, 40000, 512), (1, 300000, 2048), (64, 16384, 1024)])
+def test_decode_steps_with_survivor_hand_over(oracle, B, L, k_top):
+    """The producer lists every score not below the row's guess; a row whose guess fits is ranked
+    from the list alone.  Steps: no guess yet (lists empty, select from the scores), guesses hit
+    (same queries), a jump (too many listed: miss, select from the scores), hit again; one row
+    is at times no longer than k.  Exact every step; the list headers come back zeroed."""
+    from flash_float_jit_kernels_b200 import _lib, new_threshold_hint
+    from flash_float_jit_kernels_b200.indexer_logits import indexer_topk, new_handover
+    dev = torch.device("cuda:0")
+    q, k, w = _make(B, L, 31 + B, dev)
+    kd, wd = k.to(dev), w.to(dev)
+    scores = torch.full((B, L), float("-inf"), device=dev)
+    out = torch.empty((B, k_top), dtype=torch.int32, device=dev)
+    hint = new_threshold_hint(B, dev)
+    handover = new_handover(B, dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    kf = k.float().numpy()
+    seen = []
+    for step in range(5):
+        qs = q.float()
+        if step >= 3:
+            qs = qs * 2.0                      # every score doubles (and stays so): the old guesses let far too many through
+        qs = qs.to(torch.float8_e4m3fn)
+        lens = [L - 128 * step - 5] + [max(k_top + 1, L // (2 + b)) + 64 * step for b in range(1, B)]
+        if B > 1 and step in (2, 4):
+            lens[1] = k_top - 3                # a row no longer than k: identity order, its list header is cleared
+        lengths = torch.tensor(lens, dtype=torch.int32)
+        status.zero_()
+        indexer_topk(qs.to(dev), kd, wd, lengths.to(dev), k_top, scores=scores, out=out, threshold_hint=hint,
+                     status=status, handover=handover)
+        torch.cuda.synchronize()
+        seen.append(int(status.item()))
+        exp_scores = np.full((B, L), -np.inf, dtype=np.float32)
+        for b in range(min(B, 4)):             # the oracle's own scores for the first rows, the produced ones for the rest
+            n = lens[b]
+            exp_scores[b, :n] = oracle.indexer_logits(qs[b].float().numpy(), kf[b, :n], w[b].numpy())[0]
+        got_scores = scores.cpu().numpy()
+        for b in range(4, B):
+            exp_scores[b, :lens[b]] = got_scores[b, :lens[b]]
+        assert np.array_equal(out.cpu().numpy(), oracle.topk_c(exp_scores, lengths.numpy(), k_top)), step
+        hdr = handover.view(torch.int32).view(B, _lib.FF_TOPK_HANDOVER_ROW_BYTES // 4)[:, :2].cpu()
+        assert int(hdr.abs().sum()) == 0, f"step {step}: list headers not cleared: {hdr.tolist()[:4]}"
+    assert seen[0] == 0, "no guesses yet: nothing can miss"
+    assert seen[1] == 0, "guesses from the first step fit the second"
+    assert seen[3] == _lib.FF_STATUS_HINT_MISSED, "doubled scores: the lists overflow, the select falls back"
+    assert seen[4] == 0
