@@ -65,7 +65,7 @@ struct Params {
 };
 
 constexpr int kHandoverCap = 4096;       // entries per row (the select's survivor capacity)
-constexpr int kHandoverWarpBuf = 64;     // composites an epilogue warp collects before it reserves list slots
+constexpr int kHandoverWarpBuf = 64;     // composites an epilogue warp collects in one of its two buffers
 
 // Order-preserving fp32 -> uint32 map, the same as the select's (-0.0 == +0.0, NaN on top).
 __device__ __forceinline__ uint32_t monotone_key(float x) {
@@ -77,14 +77,10 @@ __device__ __forceinline__ uint32_t monotone_key(float x) {
   return k;
 }
 
-// An epilogue warp moves its collected composites into the row's hand-over list: one global atomic
-// reserves the slots (so the round trip is paid once per about 32 survivors, not per tile), two
-// stores per lane fill them; what does not fit the list is dropped (the count tells the select).
-__device__ __forceinline__ void flush_handover(unsigned char* row_base, const unsigned long long* buf, int n, int lane) {
-  if (n == 0) return;
-  uint32_t base = 0;
-  if (lane == 0) base = atomicAdd(reinterpret_cast<uint32_t*>(row_base), static_cast<uint32_t>(n));
-  base = __shfl_sync(0xffffffffu, base, 0);
+// An epilogue warp moves collected composites into the row's hand-over list at the slots it
+// reserved (two stores per lane); what does not fit the list is dropped (the count tells the select).
+__device__ __forceinline__ void store_handover(unsigned char* row_base, const unsigned long long* buf, int n,
+                                               uint32_t base, int lane) {
   unsigned long long* list = reinterpret_cast<unsigned long long*>(row_base + 64);
   for (int i = lane; i < n; i += 32)
     if (base + i < static_cast<uint32_t>(kHandoverCap)) list[base + i] = buf[i];
@@ -220,7 +216,7 @@ struct Shared {
   uint32_t tmem_base;
   int timed_out;
   float w[kHeads];
-  unsigned long long handover[kEpilogueWarps][kHandoverWarpBuf];   // per epilogue warp: survivors not yet in the list
+  unsigned long long handover[kEpilogueWarps][2][kHandoverWarpBuf];   // per epilogue warp: survivors not yet in the list
 };
 
 __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Params p) {
@@ -329,8 +325,14 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Param
     if (p.hint != nullptr && p.handover != nullptr) hint = p.hint[row];
     const bool hand_over = hint == hint;
     unsigned char* row_base = p.handover + static_cast<int64_t>(row) * FF_HANDOVER_ROW_BYTES;
-    unsigned long long* mine = sh.handover[warp];
-    int n_mine = 0;   // uniform over the warp
+    // Two buffers per warp.  When the one being filled may not hold another tile's hits, lane 0
+    // reserves list slots for it with one global atomic and the warp switches to the other buffer;
+    // the reserved position is looked at a tile later, when the full buffer is stored, so the
+    // atomic's round trip overlaps the next tile instead of stalling the epilogue (the accumulator
+    // buffers give the epilogue only one tile of slack).
+    int cur = 0, n_cur = 0;          // uniform over the warp
+    int n_pending = 0;               // entries of the other buffer whose slots are reserved but not stored
+    uint32_t pending_base = 0u;      // lane 0: result of that reservation
     for (int i = 0; i < my_tiles; ++i) {
       const int buf = i & 1;
       (void)mbar_wait(smem_u32(&sh.tfull[buf]), static_cast<uint32_t>((i / 2) & 1), &sh.timed_out);
@@ -342,25 +344,36 @@ __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Param
       const int key = (cta + i * n_ctas) * kTileKeys + key_in_tile;
       if (key < p.L_width) out_row[key] = key < len ? s : __uint_as_float(0xff800000u);
       if (hand_over) {
+        if (n_pending > 0) {   // last tile's reservation has long arrived
+          store_handover(row_base, sh.handover[warp][cur ^ 1], n_pending, __shfl_sync(0xffffffffu, pending_base, 0), lane);
+          n_pending = 0;
+        }
         const bool hit = key < len && !(s < hint);
         const uint32_t votes = __ballot_sync(0xffffffffu, hit);
         if (votes != 0u) {
           if (hit)
-            mine[n_mine + __popc(votes & ((1u << lane) - 1u))] =
+            sh.handover[warp][cur][n_cur + __popc(votes & ((1u << lane) - 1u))] =
                 (static_cast<unsigned long long>(monotone_key(s)) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(key));
-          n_mine += __popc(votes);
-          if (n_mine > kHandoverWarpBuf - 32) {   // the next tile might not fit: reserve list slots now
+          n_cur += __popc(votes);
+          if (n_cur > kHandoverWarpBuf - 32) {   // the next tile might not fit: reserve list slots, switch buffers
             __syncwarp();
-            flush_handover(row_base, mine, n_mine, lane);
-            __syncwarp();
-            n_mine = 0;
+            if (lane == 0) pending_base = atomicAdd(reinterpret_cast<uint32_t*>(row_base), static_cast<uint32_t>(n_cur));
+            n_pending = n_cur;
+            cur ^= 1;
+            n_cur = 0;
           }
         }
       }
     }
     if (hand_over) {
       __syncwarp();
-      flush_handover(row_base, mine, n_mine, lane);
+      if (n_pending > 0)
+        store_handover(row_base, sh.handover[warp][cur ^ 1], n_pending, __shfl_sync(0xffffffffu, pending_base, 0), lane);
+      if (n_cur > 0) {
+        uint32_t base = 0u;
+        if (lane == 0) base = atomicAdd(reinterpret_cast<uint32_t*>(row_base), static_cast<uint32_t>(n_cur));
+        store_handover(row_base, sh.handover[warp][cur], n_cur, __shfl_sync(0xffffffffu, base, 0), lane);
+      }
     }
   }
   tc_fence_before();
