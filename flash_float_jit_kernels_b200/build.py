@@ -30,7 +30,10 @@ NVCC_FLAGS = [
 
 
 def lib_path() -> Path:
-    return CSRC / LIB_NAME
+    flags = env_flags()
+    if not flags:
+        return CSRC / LIB_NAME
+    return CSRC / LIB_NAME.replace(".so", _knob_suffix(flags) + ".so")
 
 
 def indexer_lib_path() -> Path:
@@ -57,6 +60,25 @@ def is_stale() -> bool:
     return any(d.stat().st_mtime > t for d in deps if d.exists())
 
 
+def env_flags():
+    """Compile-time knobs taken from the environment, as ``-D`` flags (the reference does the same
+    with its ``FLASH_FLOAT_TOPK_*`` variables, ``jit_kernel/topk_indexer.py:11-48``):
+    ``FF_TOPK_TILE_UNITS`` (16-byte units per shared-memory tile, a multiple of 512 up to 4096) and
+    ``FF_TOPK_EXTRA_NVCC_FLAGS`` (anything else, space separated).  A library built with knobs gets
+    them into its file name, so that it never replaces the default build."""
+    flags = []
+    tile = os.environ.get("FF_TOPK_TILE_UNITS")
+    if tile:
+        flags.append(f"-DFF_TOPK_TILE_UNITS={int(tile)}")
+    flags += os.environ.get("FF_TOPK_EXTRA_NVCC_FLAGS", "").split()
+    return flags
+
+
+def _knob_suffix(flags) -> str:
+    import hashlib
+    return "" if not flags else "_" + hashlib.sha1(" ".join(flags).encode()).hexdigest()[:8]
+
+
 def _compile(out: Path, sources, verbose: bool, extra_flags) -> Path:
     cmd = [_nvcc(), *NVCC_FLAGS, *extra_flags]
     if verbose:
@@ -75,7 +97,7 @@ def build_library(force: bool = False, verbose: bool = False, extra_flags=()) ->
     out = lib_path()
     if not force and not is_stale():
         return out
-    return _compile(out, SOURCES, verbose, extra_flags)
+    return _compile(out, SOURCES, verbose, [*env_flags(), *extra_flags])
 
 
 CHECKED_LIB_NAME = "libff_topk_checked.so"   # the same library compiled with -DFF_BOUNDS_CHECK

@@ -44,7 +44,10 @@ constexpr int kSmemRing = kSmemSort + kSortCap * 8;            // ring of score 
 constexpr int kSmemCand = kSmemRing;                           // uint64[kCandCap]: deeper levels only, after the ring's last use
 // One bulk copy costs about 0.3 us on top of its transfer time and an SM runs
 // them one after the other (measured), so tiles are as large as shared memory allows.
-constexpr int kTileUnits = 4096;                               // 16-byte units per tile (64 KiB)
+#ifndef FF_TOPK_TILE_UNITS
+#define FF_TOPK_TILE_UNITS 4096
+#endif
+constexpr int kTileUnits = FF_TOPK_TILE_UNITS;                 // 16-byte units per tile (64 KiB); a build-time knob for A/B runs
 constexpr int kTileBytes = kTileUnits * 16;
 static_assert(kTileUnits % kThreads == 0 && kTileUnits / kThreads <= 8, "a thread reads at most 8 units of a tile");
 constexpr int kStages = 2;                                     // tiles in the ring (128 KiB)
@@ -52,7 +55,12 @@ constexpr int kMinStages = kStages;
 constexpr int kMaxStages = kStages;
 constexpr int kWaitLimit = 1 << 22;                            // bounded mbarrier polling
 
-__host__ __device__ constexpr int smem_bytes_for(int stages) { return kSmemRing + stages * kTileBytes; }
+// The ring's region also holds the finish's work arrays (106 KiB) and the context-parallel merge's
+// staged runs (up to 128 KiB), so it never shrinks below 128 KiB whatever the tile size.
+constexpr int kMinRingBytes = 128 * 1024;
+__host__ __device__ constexpr int smem_bytes_for(int stages) {
+  return kSmemRing + (stages * kTileBytes > kMinRingBytes ? stages * kTileBytes : kMinRingBytes);
+}
 
 // ---- distributed shared memory primitives (PTX) ------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
