@@ -108,6 +108,7 @@ FF_STATUS_WAIT_TIMEOUT = 2
 FF_STATUS_HINT_MISSED = 8
 FF_STATUS_CP_SECOND_ROUND = 16
 FF_STATUS_BOUNDS = 32
+FF_STATUS_CP_SX_FALLBACK = 64
 TRACE_SLOTS = 40
 
 

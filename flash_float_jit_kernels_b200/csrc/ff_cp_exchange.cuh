@@ -57,6 +57,14 @@ __device__ __forceinline__ uint2 ld_entry(const uint32_t* entry) {
   asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(w) : "l"(entry) : "memory");
   return make_uint2(static_cast<uint32_t>(w), static_cast<uint32_t>(w >> 32));
 }
+// Both words of an entry with one 16-byte request: {payload0, step0, payload1, step1}.  The two
+// halves are validated separately (each 64-bit half is written whole).
+__device__ __forceinline__ uint4 ld_entry_pair(const uint32_t* entry) {
+  unsigned long long a, b;
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(entry) : "memory");
+  return make_uint4(static_cast<uint32_t>(a), static_cast<uint32_t>(a >> 32), static_cast<uint32_t>(b),
+                    static_cast<uint32_t>(b >> 32));
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -65,6 +73,21 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Polls the entry until it carries `step`; gives up (ok = false, payload = no candidate) when
 // more than kPeerWaitNs have passed since t0.
+// Polls both halves of an entry until each carries `step`, pausing between polls so that many
+// waiting threads do not keep the writers out of the memory system; gives up like await_entry.
+__device__ __forceinline__ uint2 await_entry_pair(const uint32_t* entry, uint4 first, uint32_t step,
+                                                  unsigned long long t0, bool& ok) {
+  uint4 e = first;
+  while (e.y != step || e.w != step) {
+    if (global_ns() - t0 > kPeerWaitNs) {
+      ok = false;
+      return make_uint2(kNoCandidateBits, 0xffffffffu);
+    }
+    __nanosleep(100);
+    e = ld_entry_pair(entry);
+  }
+  return make_uint2(e.x, e.z);
+}
 __device__ __forceinline__ uint32_t await_entry(const uint32_t* entry, uint2 first, uint32_t step,
                                                 unsigned long long t0, bool& ok) {
   uint2 e = first;

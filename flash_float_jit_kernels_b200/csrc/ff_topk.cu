@@ -4,6 +4,7 @@
 #include "../../include/ff_topk.h"
 
 #include <atomic>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -602,6 +603,7 @@ struct FfCpExchange {
   size_t slot_words;     // one rank's candidate block: a 16-byte entry per (row, position) (4*B*k words)
   size_t ctrl_offset;    // words from the allocation's start to the control words
   size_t send_offset;    // words from the allocation's start to the send block
+  size_t sx_offset;      // words from the allocation's start to the survivor-exchange regions
   size_t total_bytes;
   uint32_t* base;        // this rank's allocation
   void* peer[ff::kMaxPeers];
@@ -625,7 +627,10 @@ int ff_cp_exchange_create(int32_t world, int32_t rank, int32_t B, int32_t k, voi
   ex->slot_words = 4 * static_cast<size_t>(B) * k;
   ex->ctrl_offset = 2 * static_cast<size_t>(world) * ex->slot_words;
   ex->send_offset = ex->ctrl_offset + ff::kCtrlWords;
-  ex->total_bytes = (ex->send_offset + ex->slot_words) * sizeof(uint32_t);
+  ex->sx_offset = ex->send_offset + ex->slot_words;
+  // survivor exchange: two step parities x world sending ranks x B rows x 128 regions of 528 bytes
+  const size_t sx_words = 2 * static_cast<size_t>(world) * B * ff::kSxRegions * ff::kSxRegionWords;
+  ex->total_bytes = (ex->sx_offset + sx_words) * sizeof(uint32_t);
   for (int i = 0; i < ff::kMaxPeers; ++i) {
     ex->peer[i] = nullptr;
     ex->opened[i] = false;
@@ -723,6 +728,25 @@ int cp_prefix(int world, int k) {
   return s < k ? (s < 1 ? 1 : s) : k;
 }
 
+// Whether a single-kernel step of `world` ranks first tries the exchange of survivors (every rank
+// makes a guess for the whole row from its own shard and all finish from the same survivor list)
+// before the exchange of sorted runs.  It needs the rows' own guesses (ff_topk_set_self_seed) and is
+// not used when the caller carries guesses for the shards (those mean something else: a score
+// between the SHARD's k-th and 4096-th largest).  Off unless FF_TOPK_CP_SX=1: on 4 GPUs it measured
+// 21.9 us per step against 19.0 us with sorted runs (all 120 CTAs of a rank read every rank's regions,
+// 14 MB through L2 per step); it is kept, exact and tested, for rows where ranking before the
+// exchange costs more than here.  Every rank must decide alike, which they do when they make the
+// same calls with the same settings.
+int cp_survivor_exchange(int world, bool caller_hints, int k, int ctas_per_row) {
+  if (world < 2 || caller_hints || !self_seed_enabled()) return 0;
+  const char* on = getenv("FF_TOPK_CP_SX");
+  if (on == nullptr || atoi(on) == 0) return 0;
+  // a CTA's region takes kSxCap survivors: expected number plus six standard deviations must fit
+  const double per_cta = 1.5 * k / (static_cast<double>(world) * ctas_per_row);
+  if (ctas_per_row > ff::kSxRegions || per_cta + 6.0 * sqrt(per_cta) > ff::kSxCap) return 0;
+  return 1;
+}
+
 // The parameter block of one rank's context-parallel send launch (shared by the real entry points
 // and the several-ranks-in-one-launch test entry).  Returns 0 and the cluster size.
 int cp_fill_params(FfCpExchange* ex, const float* scores, int64_t row_stride, const int32_t* lengths,
@@ -753,6 +777,8 @@ int cp_send_impl(void* handle, const float* scores, int64_t row_stride, const in
     if (log2c < 5 && clusters <= g_active_clusters[device][log2c]) {
       p.push_fused = 1;
       p.push_prefix = cp_prefix(ex->world, ex->k);   // only a launch that merges itself can ask for the rest
+      p.push_sx = cp_survivor_exchange(ex->world, hint_in != nullptr || hint_out != nullptr, ex->k,
+                                       cluster * (p.groups > 1 ? p.groups : 1));
       p.out_idx = fused_out;
       if (did_fuse != nullptr) *did_fuse = true;
     }
@@ -791,6 +817,7 @@ int cp_fill_params(FfCpExchange* ex, const float* scores, int64_t row_stride, co
   p.push_slot_words = static_cast<int64_t>(ex->slot_words);
   p.push_ctrl_offset = static_cast<int64_t>(ex->ctrl_offset);
   p.push_prefix = ex->k;   // a send whose merge is another launch delivers whole runs
+  p.push_sx_offset = static_cast<int64_t>(ex->sx_offset);
   p.hint_in = hint_in;     // guesses of the shard-local threshold, as in ff_topk_launch_hinted
   p.hint_out = hint_out;
   int cluster = choose_cluster(device, ex->B, L_width, ex->k);
@@ -889,6 +916,7 @@ int ff_topk_cp_step_emulated_ranks(int32_t n_ranks, void* const* handles, const 
     }
     e.rank[r].push_fused = 1;
     e.rank[r].push_prefix = cp_prefix(n_ranks, ex->k);
+    e.rank[r].push_sx = cp_survivor_exchange(n_ranks, hint != nullptr, ex->k, c * g);
     e.rank[r].out_idx = out_idx[r];
     e.rank[r].trace = g_trace.load(std::memory_order_relaxed);
   }

@@ -129,6 +129,8 @@ struct TopkParams {
   int64_t push_slot_words;
   int64_t push_ctrl_offset;    // words from an exchange buffer's start to its control words
   int32_t push_fused;          // 1: the same launch also waits for the peers and merges (single-kernel step)
+  int32_t push_sx;             // 1: the step first tries the exchange of survivors (needs push_fused)
+  int64_t push_sx_offset;      // words from an exchange buffer's start to its survivor-exchange regions
   int32_t push_prefix;         // candidates per row sent to the peers right away (the first push_prefix of the k);
                                // the rest stay in this rank's own slot until a merge finds that it needs them
   int32_t block_base;          // first CTA of this rank's part of the grid (0 except when several ranks are

@@ -917,6 +917,12 @@ __device__ __forceinline__ void merge_two_step(cg::cluster_group& cluster, int C
   FF_TRACE(p, 30);
 }
 
+// Context-parallel exchange of survivors: regions of one (step parity, sending rank, row).
+constexpr int kSxRegions = 128;                 // one per CTA of the sending rank's row (unused ones are sent empty)
+constexpr int kSxCap = 64;                      // entries per region
+constexpr int kSxRegionWords = 4 + 4 * kSxCap;  // header {count | flags, step, guess key, step} + 16-byte entries
+constexpr uint32_t kSxFallbackFlag = 1u << 16;
+
 // ---- a row seeds its own threshold guess ----------------------------------------------------
 // A threshold guess (a score between the row's k-th and 4096-th largest) lets the row be selected in
 // one sweep without histogram, merge or second sweep.  When the caller has none and the row is
@@ -937,12 +943,21 @@ struct SeedPlan {
   int n_use;       // 16-byte units of a CTA's first tile that it looks at
 };
 // Row-level decision, from quantities every CTA of the row computes alike.
-__device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, int n_share, int k) {
+// len_for_p: the length the target count refers to (the whole row's in a context-parallel step,
+// where `len` is the shard's).
+__device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, int n_share, int k, int len_for_p = 0,
+                                              int ranks = 1) {
   SeedPlan sp;
   sp.use = false;
-  const int target = min(k + (k >> 2) + 64, kSortCap - (kSortCap >> 3));   // hint_target_rank(k)
-  sp.p = static_cast<float>(target) / static_cast<float>(len);
-  if (n_share > kThreads || len < 4 * target) return sp;   // (the accumulator's counters hold up to 1023)
+  // hint_target_rank(k) for one rank.  Several ranks' guesses side by side: the list must hold k
+  // entries not below the LARGEST guess, which sits a standard deviation or two above the rest, so
+  // aim half-way between k and the list's capacity.
+  const int target = ranks > 1 ? min(k + (k >> 1), kSortCap - (kSortCap >> 3))
+                               : min(k + (k >> 2) + 64, kSortCap - (kSortCap >> 3));
+  if (len_for_p <= 0) len_for_p = len;
+  sp.p = static_cast<float>(target) / static_cast<float>(len_for_p);
+  sp.n_use = 0;
+  if (n_share > kThreads || len_for_p < 4 * target) return sp;   // (the accumulator's counters hold up to 1023)
   const int U = static_cast<int>((static_cast<int64_t>(len) + mis + per_unit - 1) / per_unit);
   const int per = (U + n_share - 1) / n_share;          // units per CTA, as make_chunk cuts them
   int n0 = min(per, kTileUnits);                        // units of a CTA's first tile
@@ -963,7 +978,11 @@ __device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, in
   // a usable order statistic inside the kept 32, and enough hits over the row for a steady mean
   // (relative noise of the row's survivor count about 1.25 / sqrt(hits): 6 % at 400 hits, against a
   // window of -22 % .. +56 % around the target)
-  sp.use = rho >= 3.f && rho <= 30.f && rho * static_cast<float>(n_share) >= 400.f;
+  // In a context-parallel step the `ranks` guesses are used side by side (every rank's own
+  // for its own shard), so the row's count averages over all of them; a single rank's guess may be
+  // noisier (it only shifts the largest guess, which the final check allows for).
+  const float hits = rho * static_cast<float>(n_share);
+  sp.use = rho >= 3.f && rho <= 30.f && hits * static_cast<float>(ranks) >= 400.f && hits >= 100.f;
   return sp;
 }
 
@@ -1042,9 +1061,16 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
     if (lanes >= 32) {
       const float g = static_cast<float>(kPU) * static_cast<float>(n0) / static_cast<float>(lanes);
       const float rho = static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-p_frac)));
-      const int r = min(max(static_cast<int>(rho + 0.5f), 1), 32);
-      const uint32_t key = sorted[r - 1];
-      // (keys above +inf's are NaN patterns, key 0 means fewer than r threads had a score: no estimate)
+      // The (i+1)-th largest maximum has i + 1 maxima at or above it; the MEAN over the CTAs of the
+      // score at a random such count sits where the count is about half a step smaller (the tail
+      // is convex), so the estimate is read at the fractional position rho - 0.5 (0-based),
+      // between two neighbours of the sorted list, which also removes the rounding of rho.
+      const float pos = fminf(fmaxf(rho - 0.5f, 0.f), 30.99f);
+      const int i0 = static_cast<int>(pos);
+      const uint32_t k0 = sorted[i0], k1 = sorted[i0 + 1];
+      uint32_t key = k0;
+      if (k1 != 0u && k1 <= k0) key = k0 - static_cast<uint32_t>((pos - static_cast<float>(i0)) * static_cast<float>(k0 - k1));
+      // (keys above +inf's are NaN patterns, key 0 means too few threads had a score: no estimate)
       if (key != 0u && key <= 0xff800000u) add |= (1ull << 44) | key;
     }
     atomicAdd(acc, add);
@@ -1087,7 +1113,7 @@ struct PushCtx {
 // In push mode (context-parallel send) the slot is not written locally at all: the (value,
 // global index) pair goes straight into this rank's slot of every peer's receive buffer.
 
-template <bool PUSH>
+template <bool PUSH, bool VALUES = true>
 __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, int row, int j, int32_t idx,
                                      uint32_t key, bool is_map, int table_row) {
   if (PUSH) {
@@ -1117,7 +1143,7 @@ __device__ __forceinline__ void emit(const TopkParams& p, const PushCtx& push, i
   if (!FF_IN_RANGE(p, j, p.k, 9) || !FF_IN_RANGE(p, row, p.B, 10)) return;
   if (p.out_idx64 != nullptr) p.out_idx64[static_cast<int64_t>(row) * p.k + j] = o;
   else p.out_idx[static_cast<int64_t>(row) * p.k + j] = o;
-  if (p.out_val != nullptr) {
+  if (VALUES && p.out_val != nullptr) {
     p.out_val[static_cast<int64_t>(row) * p.k + j] =
         idx < 0 ? __uint_as_float(0xff800000u) : __uint_as_float(bits_of_key(key));
   }
@@ -1138,8 +1164,10 @@ constexpr int kModeHinted = 1;
 constexpr int kModePush = 2;
 constexpr int kModePushHinted = kModePush | kModeHinted;
 
+// Returns true when the row's output has been written by the survivor exchange of a
+// context-parallel step (then the caller has no runs to merge).
 template <bool HAS_MAP, int MODE, typename T>
-__device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
+__device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char* smem, ClusterShared& sh,
                                               const PushCtx& push) {
   static_assert(!HAS_MAP || Elem<T>::kPerUnit == 4, "merge mode selects among fp32 candidates");
   constexpr int kPU = Elem<T>::kPerUnit;
@@ -1194,7 +1222,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
 
   // ---- short rows: nothing to select --------------------------------------
   const bool identity = HAS_MAP ? (glen <= k) : (len <= k);
-  if (identity || len <= k) {
+  const bool is_short = identity || len <= k;
+  auto short_row_path = [&]() {
     if (my_share != 0) return;
     if (kHinted && !HAS_MAP && p.handover != nullptr && tid == 0) {
       // nobody reads this row's hand-over list in this launch: leave its header zeroed for the next producer
@@ -1235,10 +1264,19 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       }
     }
     return;
+  };
+  // A context-parallel step whose ranks exchange survivors (below) needs every rank, also one whose
+  // shard is short, to take part in the exchange.
+  const bool sx_try = kPush && kHinted && !HAS_MAP && p.push_sx != 0 && p.push_fused != 0 && glen > k;
+  if (is_short && !sx_try) {
+    short_row_path();
+    return false;
   }
 
   const Chunk<T> chunk = make_chunk<T>(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
+  bool hinted_done_sx = false;   // set by the survivor exchange of a context-parallel step
+  int expected_total_sx = 0;
 
   TileStream ts;
   ts.src = reinterpret_cast<const float4*>(chunk.abase) + chunk.fb;
@@ -1262,12 +1300,220 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     }
   }
 
+  // ---- context-parallel step by exchange of survivors ----------------------------------------
+  // Instead of ranking its own candidates, sending the sorted run and merging runs, every rank
+  // makes a guess of the score that about 1.25 k + 64 scores of the WHOLE row reach (from its own
+  // shard: seed_own_guess with p = target / global length), collects what its shard holds at or
+  // above it, and every CTA stores its few survivors straight into a region of its own in every
+  // rank's buffer (header {count, flags, guess} + entries, all self-validating with the step).
+  // Every CTA of every rank then reads all regions in the same order, so all hold the same list of
+  // about 1.25 k survivors and finish it exactly like a one-GPU row whose guess fitted: no local
+  // ranking before the exchange, no run merge after it.  The list holds the row's whole top-k if at
+  // least k of its entries are not below the LARGEST of the ranks' guesses (what a rank did not send
+  // is below its own guess).  Otherwise (a rank without a guess, too many survivors in one CTA, too
+  // few or too many in all) every rank sees the same evidence and all fall back to the exchange of
+  // sorted runs.  A rank whose shard is small sends all of it (guess "none").
+  bool sx_done = false;
+  if constexpr (kPush && kHinted && !HAS_MAP) {
+    if (sx_try) {
+      __syncthreads();   // the set-up above (counters, mbarriers) is visible to every thread
+      const int world = p.push_world;
+      const uint32_t step = push.step;
+      bool fallback = n_share > kSxRegions;
+      uint32_t hkey = 0u;
+      int n_mine = 0;
+      if (!fallback && len <= kSxCap * n_share) {
+        // small shard: CTA c sends elements [c * cap, (c + 1) * cap)
+        const int b0 = my_share * kSxCap;
+        n_mine = min(max(len - b0, 0), kSxCap);
+        if (tid < n_mine) stage[tid] = make_comp(key_of(Elem<T>::to_float(rowp[b0 + tid])), b0 + tid);
+      } else if (!fallback) {
+        const SeedPlan sp = seed_plan(len, chunk.mis, kPU, n_share, k, glen, world);
+        if (!sp.use || G <= 1) {
+          fallback = true;
+        } else {
+          const int n0 = ts.n_tiles > 0 ? tile_units(ts, 0) : 0;
+          if (n0 > 0) {
+            stream_fetch(ts, 0);
+            if (!mbar_wait(ts.bars, static_cast<uint32_t>(ts.fidx0 & 1))) ts.timed_out = true;
+            ts.arrived0 = true;
+          }
+          const SeedResult sr = seed_own_guess<T>(ts.ring, min(n0, sp.n_use), &sh.flag, hist, ws, sp.p, n_share, my_share);
+          if (sr.code == 2) ts.timed_out = true;
+          FF_TRACE(p, 21);
+          if (sr.code != 1) {
+            fallback = true;
+          } else {
+            const float guess = sr.guess;
+            hkey = key_of(guess);
+            stream_pass(ts, [&](uint32_t tile, int tt, int units) {
+              collect_tile<T>(tile, units, chunk.fb + tt * kTileUnits, chunk.mis, guess, stage, kSortCap, &sh.stage_count);
+            });
+            float x = 0.f;
+            const int pos = partial_element(chunk, x);
+            if (pos >= 0 && !(x < guess)) {
+              const int slot = atomicAdd(&sh.stage_count, 1);
+              if (slot < kSortCap) stage[slot] = make_comp(key_of(x), pos);
+            }
+            __syncthreads();
+            n_mine = sh.stage_count;
+            if (n_mine > kSxCap) {   // a crowded chunk: this protocol is not for such rows
+              fallback = true;
+              n_mine = 0;
+            }
+          }
+        }
+      }
+      __syncthreads();
+      FF_TRACE(p, 3);
+      // ---- send: entries and header of this CTA's region to every rank (own rank included) ----
+      auto region_in = [&](uint32_t* base, int src_rank, int c) {
+        return base + p.push_sx_offset +
+               ((((static_cast<size_t>(step & 1u) * world + src_rank) * p.B + row) * kSxRegions) + c) * kSxRegionWords;
+      };
+      if (my_share < kSxRegions) {
+        for (int i = tid; i < world * n_mine; i += kThreads) {
+          const int q = i / n_mine, e = i - q * n_mine;
+          const uint64_t c = stage[e];
+          st_entry(region_in(p.push_peers.base[q], p.push_rank, my_share) + 4 + 4 * e, bits_of_key(comp_key(c)),
+                   static_cast<uint32_t>(comp_index(c) + p.shard_offset), step);
+        }
+        const uint32_t head = static_cast<uint32_t>(n_mine) | (fallback ? kSxFallbackFlag : 0u);
+        if (tid < world) st_entry(region_in(p.push_peers.base[tid], p.push_rank, my_share), head, hkey, step);
+        if (my_share == 0) {   // the regions no CTA of this launch owns: empty, same flags
+          const int spare = kSxRegions - min(n_share, kSxRegions);
+          for (int i = tid; i < world * spare; i += kThreads)
+            st_entry(region_in(p.push_peers.base[i / spare], p.push_rank, n_share + i % spare),
+                     fallback ? kSxFallbackFlag : 0u, 0u, step);
+        }
+      }
+      // ---- receive: all regions of all ranks, in region order, into the survivor list ----
+      uint32_t* pre = hist;                      // [world * kSxRegions + 1] entries before each region
+      const int R = world * kSxRegions;
+      const int J = (R + kThreads - 1) / kThreads;   // consecutive regions per thread (at most 4)
+      const unsigned long long t0 = global_ns();
+      bool sx_ok = true;
+      uint32_t cnt[4] = {0u, 0u, 0u, 0u};
+      uint32_t hmax = 0u, any_flag = 0u;
+      {
+        uint4 h[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = tid * J + j;
+          if (j < J && rr < R)
+            h[j] = ld_entry_pair(region_in(p.push_peers.base[p.push_rank], rr / kSxRegions, rr % kSxRegions));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = tid * J + j;
+          if (j < J && rr < R) {
+            const uint32_t* reg = region_in(p.push_peers.base[p.push_rank], rr / kSxRegions, rr % kSxRegions);
+            const uint2 hd = await_entry_pair(reg, h[j], step, t0, sx_ok);
+            const uint32_t head = hd.x, hk = hd.y;
+            if (sx_ok) {
+              cnt[j] = head & 0xffffu;
+              any_flag |= head & kSxFallbackFlag;
+              hmax = max(hmax, hk);
+            } else {
+              any_flag |= kSxFallbackFlag;
+            }
+          }
+        }
+      }
+      int total = 0;
+      const int mine_sum = static_cast<int>(cnt[0] + cnt[1] + cnt[2] + cnt[3]);
+      const int after = block_suffix_exclusive(mine_sum, sh.warp_tot, total);   // entries of the regions after mine
+      {
+        int before = total - after - mine_sum;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = tid * J + j;
+          if (j < J && rr < R) {
+            pre[rr] = static_cast<uint32_t>(before);
+            before += static_cast<int>(cnt[j]);
+          }
+        }
+        if (tid == 0) pre[R] = static_cast<uint32_t>(total);
+      }
+      hmax = __reduce_max_sync(0xffffffffu, hmax);
+      if ((tid & 31) == 0) sh.warp_tot[tid >> 5] = static_cast<int>(hmax);   // (the scan is done with warp_tot)
+      const bool flagged = __syncthreads_or(any_flag != 0u ? 1 : 0) != 0;
+#pragma unroll
+      for (int wi = 0; wi < kWarps; ++wi) hmax = max(hmax, static_cast<uint32_t>(sh.warp_tot[wi]));
+      FF_TRACE(p, 38);
+      bool good = !flagged && total >= k && total <= kSortCap;
+      int not_below = 0;
+      if (good) {
+        // every thread copies the entries of its own regions to their places in the list, eight
+        // entries (sixteen loads) in flight at a time
+        constexpr int kBatch = 8;
+#pragma unroll 1
+        for (int j = 0; j < J; ++j) {
+          const int rr = tid * J + j;
+          if (rr >= R) break;
+          const int n_r = static_cast<int>(j == 0 ? cnt[0] : j == 1 ? cnt[1] : j == 2 ? cnt[2] : cnt[3]);
+          const uint32_t* reg = region_in(p.push_peers.base[p.push_rank], rr / kSxRegions, rr % kSxRegions) + 4;
+          const int at = static_cast<int>(pre[rr]);
+#pragma unroll 1
+          for (int e0 = 0; e0 < n_r; e0 += kBatch) {
+            uint4 ev[kBatch];
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u)
+              if (e0 + u < n_r) ev[u] = ld_entry_pair(reg + 4 * (e0 + u));
+#pragma unroll
+            for (int u = 0; u < kBatch; ++u) {
+              if (e0 + u < n_r) {
+                const uint2 en = await_entry_pair(reg + 4 * (e0 + u), ev[u], step, t0, sx_ok);
+                const uint32_t key = key_of_bits(en.x);
+                sortbuf[at + e0 + u] = make_comp(key, static_cast<int32_t>(en.y));
+                not_below += key >= hmax ? 1 : 0;
+              }
+            }
+          }
+        }
+        if (tid == 0) sh.cand_count = 0;
+        __syncthreads();
+        not_below = __reduce_add_sync(0xffffffffu, not_below);
+        if ((tid & 31) == 0 && not_below != 0) atomicAdd(&sh.cand_count, not_below);
+        good = __syncthreads_and(sx_ok ? 1 : 0) != 0;
+        good = good && sh.cand_count >= k;   // what no rank sent is below the largest guess, and k entries are not
+        __syncthreads();
+      }
+      if (!sx_ok) ts.timed_out = true;
+      FF_TRACE(p, 39);
+      if (tid == 0) {
+        sh.stage_count = 0;
+        sh.cand_count = 0;
+      }
+      if (good) {
+        sx_done = true;
+        hinted_done_sx = true;
+        expected_total_sx = total;
+        if (my_share == 0 && tid == 0) sh.sort_count = total;
+      } else {
+        if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 64);
+        if (is_short) {
+          __syncthreads();
+          short_row_path();
+          return false;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  // Writes output slot `pos`: to the peers' slots in a context-parallel send, straight to the
+  // output (the index is global already) after an exchange of survivors, else to the output.
+  auto put = [&](int pos, int32_t idx, uint32_t key) {
+    if (kPush && sx_done) emit<false, false>(p, push, row, pos, idx, key, true, table_row);
+    else emit<kPush>(p, push, row, pos, idx, key, HAS_MAP, table_row);
+  };
+
   int r = k;                // survivors still to be taken from the current candidate set
   uint64_t P = 0;           // digits fixed so far (value of comp >> shift of the last level)
   bool src_is_cand = false; // candidates live in `cand` instead of the chunk
   int cand_n = 0;
   bool ok = true;
-  int expected_total = 0;
+  int expected_total = expected_total_sx;
   int levels_used = 0;
   uint64_t floor_comp = 0;  // no survivor's composite is below this
 
@@ -1327,7 +1573,11 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   // not below h is collected in one sweep; if that is between k and 4096 elements the row is
   // finished from them directly.  Otherwise (a miss, reported as FF_STATUS_HINT_MISSED) the
   // row starts over on the histogram path below; the result is exact either way.
-  bool hinted_done = false;
+  // (see "Last use of the scratch" below)
+  constexpr int kScratchThread = 96;
+  uint32_t counted_out_before = 0u;
+  int n_plain_to_clear = 0;
+  bool hinted_done = hinted_done_sx;
   int hinted_total = 0;     // entries a hinted attempt left in its global list (rows split over clusters)
   float hint = 0.f;
   bool use_hint = false;
@@ -1370,7 +1620,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     __syncthreads();
   }
   bool self_seeded = false;
-  if (kHinted && !HAS_MAP && p.self_seed != 0 && G > 1 && !use_hint && !hinted_done && p.handover == nullptr) {
+  if (kHinted && !HAS_MAP && p.self_seed != 0 && G > 1 && !use_hint && !hinted_done && p.handover == nullptr && !sx_try) {
     const SeedPlan sp = seed_plan(len, chunk.mis, kPU, n_share, k);
     if (sp.use) {
       // the chunk's first tile (it stays in the ring for the sweep that follows)
@@ -1630,22 +1880,13 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       if (my_share == 0 && tid == 0) sh.sort_count = static_cast<int>(__ldcg(ws + 8));   // all of them have been reserved by now
     }
     __syncthreads();
-    // Last use of the scratch: the CTA that counts in last zeroes it for the next launch.
-    if (tid == 0) {
+    // Last use of the scratch: this CTA counts itself out; the CTA that does so last zeroes the
+    // scratch for the next launch.  The atomic is issued here and its result looked at only when
+    // the row is finished (leave_scratch below), so its round trip is off the critical path.
+    n_plain_to_clear = hinted_done ? 0 : (ok ? n_load : kSortCap);
+    if (tid == kScratchThread) {
       __threadfence();
-      sh.flag = atomicAdd(ws + 7, 1u) == static_cast<uint32_t>(n_share - 1) ? 1 : 0;
-    }
-    __syncthreads();
-    if (sh.flag) {
-      for (int i = tid; i < kWsHeaderWords + levels_used * kMaxBins; i += kThreads) ws[i] = 0u;
-      // the lists must read as empty for the next launch (a failed select may have left any number of entries)
-      uint32_t* lists = ws + kWsHeaderWords + kWsHistWords;
-      const int n_plain = hinted_done ? 0 : (ok ? n_load : kSortCap);
-      for (int i = tid; i < 2 * n_plain; i += kThreads) lists[i] = 0u;
-      for (int i = tid; i < 2 * hinted_total; i += kThreads) lists[kWsListWords + i] = 0u;
-      if (kHinted && p.self_seed != 0) {
-        if (tid < 2) ws[kWsSeedWord + tid] = 0u;
-      }
+      counted_out_before = atomicAdd(ws + 7, 1u);
     }
   } else if (C > 1) {
     if (!hinted_done) cluster.sync();   // every survivor has landed in every CTA's list
@@ -1654,6 +1895,21 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
   }
   FF_TRACE(p, 20);
 
+  auto leave_scratch = [&]() {
+    if (G <= 1) return;
+    if (tid == kScratchThread) sh.flag = counted_out_before == static_cast<uint32_t>(n_share - 1) ? 1 : 0;
+    __syncthreads();
+    if (sh.flag) {
+      for (int i = tid; i < kWsHeaderWords + levels_used * kMaxBins; i += kThreads) ws[i] = 0u;
+      // the lists must read as empty for the next launch (a failed select may have left any number of entries)
+      uint32_t* lists = ws + kWsHeaderWords + kWsHistWords;
+      for (int i = tid; i < 2 * n_plain_to_clear; i += kThreads) lists[i] = 0u;
+      for (int i = tid; i < 2 * hinted_total; i += kThreads) lists[kWsListWords + i] = 0u;
+      if (kHinted && p.self_seed != 0) {
+        if (tid < 2) ws[kWsSeedWord + tid] = 0u;
+      }
+    }
+  };
   if (ts.timed_out && p.status != nullptr && tid == 0) atomicOr(p.status, 2);
   if (!ok) {
     if (p.status != nullptr && tid == 0 && my_share == 0) atomicOr(p.status, 4);
@@ -1661,7 +1917,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     if (my_share == 0) {
       for (int j = tid; j < k; j += kThreads) emit<kPush>(p, push, row, j, -1, 0u, HAS_MAP, table_row);
     }
-    return;
+    leave_scratch();
+    return false;
   }
   const int n_surv = min(expected_total, kSortCap);
   const int hint_rank = min(n_surv, hint_target_rank(k)) - 1;
@@ -1704,8 +1961,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const bool valid = tid < 32 && i < n_surv;
     const uint64_t c = valid ? sortbuf[i] : ~0ull;
     const int cnt = valid ? static_cast<int>(cnt_arr[tid]) : 0;
-    if (valid && cnt < k)
-      emit<kPush>(p, push, row, cnt, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (valid && cnt < k) put(cnt, c == 0ull ? -1 : comp_index(c), comp_key(c));
     if (kHinted && !HAS_MAP && p.hint_out != nullptr) {
       // Next call's guess: the score of rank min(n_surv, target) - 1 (hint_target_rank), written by its owner.  With fewer
       // than `target` survivors that is the smallest one; its owner then extrapolates linearly below
@@ -1736,7 +1992,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
       }
     }
     FF_TRACE(p, 25);
-    return;
+    leave_scratch();
+    return sx_done;
   }
 
   // ---- finish: rank the n_surv survivors and write the first k ------------------
@@ -1903,7 +2160,7 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
     const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
-    if (pos < k) emit<kPush>(p, push, row, pos, c == 0ull ? -1 : comp_index(c), comp_key(c), HAS_MAP, table_row);
+    if (pos < k) put(pos, c == 0ull ? -1 : comp_index(c), comp_key(c));
   }
   // Next call's guess: a score of rank hint_target_rank(k), so that about that many elements (between k and
   // 4096) pass it on similar data.  With at least that many survivors it is the lower edge of the bucket
@@ -1936,6 +2193,8 @@ __device__ __forceinline__ void topk_row_body(const TopkParams& p, unsigned char
     }
   }
   FF_TRACE(p, 25);
+  leave_scratch();
+  return sx_done;
 }
 
 // One CTA's whole job for one rank: the row body, and in context-parallel send mode the step
@@ -1954,7 +2213,7 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
     push.step = *reinterpret_cast<volatile uint32_t*>(ctrl + kEpochWord) + 1u;
     push.off = (static_cast<int64_t>(push.step & 1u) * p.push_world + p.push_rank) * p.push_slot_words;
   }
-  topk_row_body<HAS_MAP, MODE, T>(p, smem, sh, push);
+  const bool written = topk_row_body<HAS_MAP, MODE, T>(p, smem, sh, push);
   if (kPush && !HAS_MAP && p.push_world > 0) {
     FF_TRACE(p, 32);
     // Every CTA read the step long ago; the one that counts itself last advances the counter.
@@ -1962,7 +2221,7 @@ __device__ __forceinline__ void topk_cta(const TopkParams& p, unsigned char* sme
     // round trip overlaps the merge instead of delaying it.
     uint32_t counted_before = 0u;
     if (threadIdx.x == 32) counted_before = atomicAdd(ctrl + kPushDoneWord, 1u);
-    if (p.push_fused != 0) {
+    if (p.push_fused != 0 && !written) {
       // Single-kernel step: merge this row's candidates right here.  All CTAs of the launch are
       // resident at once (cooperative launch), so a CTA that polls cannot keep a CTA that has
       // yet to store its entries from running.

@@ -47,6 +47,9 @@ extern "C" {
 #define FF_STATUS_CP_SECOND_ROUND 16 /* information, not an error: a context-parallel step needed the ranks' whole
                                         candidate runs, not only their first part (winners crowded into few shards) */
 
+#define FF_STATUS_CP_SX_FALLBACK 64 /* information, not an error: a context-parallel step's exchange of survivors
+                                       did not apply (a rank without a guess, a crowded chunk, too few or too
+                                       many survivors) and the step exchanged sorted runs instead */
 #define FF_STATUS_BOUNDS 32 /* only in the build with -DFF_BOUNDS_CHECK: an index fell outside its work array (the access
                                was skipped; bits 8.. name the place); the result of that launch is not to be trusted */
 
@@ -217,6 +220,15 @@ int ff_topk_cp_merge(const float* cand_val, const int32_t* cand_idx, int32_t n_r
  *   ff_topk_cp_recv_merge      wait for all peers' entries of the current step + merge (1 launch)
  *   ff_topk_cp_step            the whole step as ONE launch (select, store to peers, poll, merge) when
  *                              all CTAs of the launch can be resident at once; else send + recv_merge.
+ *                              With FF_TOPK_CP_SX=1 in the environment (off by default: it measured slower
+ *                              than what follows) and without caller's guesses the one-launch form first
+ *                              tries an exchange of SURVIVORS: every rank guesses, from its own shard, the score that about
+ *                              1.25 k + 64 scores of the whole row reach, every CTA stores the few scores of
+ *                              its chunk that reach it into a region of its own in every rank's buffer, and
+ *                              every rank finishes the same list of survivors like a one-GPU row (no local
+ *                              ranking, no run merge; exact: the list is checked to hold k entries not below
+ *                              the largest of the ranks' guesses).  Where that does not apply
+ *                              (FF_STATUS_CP_SX_FALLBACK) the step exchanges sorted runs:
  *                              In the one-launch form with more than two ranks a rank first sends only the
  *                              head of its run (2k/world candidates per row, at least 256; FF_TOPK_CP_PREFIX
  *                              overrides): the heads hold the row's whole top-k unless some head is used up

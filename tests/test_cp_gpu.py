@@ -407,7 +407,8 @@ def _emulated_step(lib, exs, shards, lengths_dev, outs, offsets, hints, wss, ws_
         status.data_ptr(), torch.cuda.current_stream().cuda_stream)
 
 
-def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=False, expect_second_round=None):
+def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=False, expect_second_round=None,
+                  survivor_exchange=True, expect_sx_fallback=None):
     """Plays P ranks of `steps` context-parallel steps in one launch each and compares every
     rank's result with the oracle on the unsharded rows.  Returns the status word of every step."""
     from flash_float_jit_kernels_b200 import _lib, new_threshold_hint, shard_bounds
@@ -417,6 +418,7 @@ def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=
     assert L % (4 * P) == 0, "equal shards, so that every rank gets the same launch shape"
     if prefix is not None:
         os.environ["FF_TOPK_CP_PREFIX"] = str(prefix)
+    os.environ["FF_TOPK_CP_SX"] = "1" if survivor_exchange else "0"   # (the library's default is off)
     lib.ff_topk_set_cluster_override(cluster)
     lib.ff_topk_set_groups_override(groups)
     exs = _make_exchanges(lib, P, B, k)
@@ -443,7 +445,10 @@ def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=
             torch.cuda.synchronize()
             bits = int(status.item())
             seen.append(bits)
-            assert bits & ~(_lib.FF_STATUS_HINT_MISSED | _lib.FF_STATUS_CP_SECOND_ROUND) == 0, f"step {step}: status {bits}"
+            info = _lib.FF_STATUS_HINT_MISSED | _lib.FF_STATUS_CP_SECOND_ROUND | _lib.FF_STATUS_CP_SX_FALLBACK
+            assert bits & ~info == 0, f"step {step}: status {bits}"
+            if expect_sx_fallback is not None:
+                assert bool(bits & _lib.FF_STATUS_CP_SX_FALLBACK) == expect_sx_fallback, f"step {step}: status {bits}"
             if expect_second_round is not None:
                 assert bool(bits & _lib.FF_STATUS_CP_SECOND_ROUND) == expect_second_round, f"step {step}: status {bits}"
             exp = oracle.topk_c(s.numpy(), lengths.numpy(), k)
@@ -452,6 +457,7 @@ def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=
     finally:
         torch.cuda.synchronize()
         os.environ.pop("FF_TOPK_CP_PREFIX", None)
+        os.environ.pop("FF_TOPK_CP_SX", None)
         lib.ff_topk_set_cluster_override(0)
         lib.ff_topk_set_groups_override(0)
         for h in exs:
@@ -461,9 +467,12 @@ def _run_emulated(oracle, P, B, L, k, make_row, steps=3, prefix=None, use_hints=
 
 @pytest.mark.parametrize("P", [2, 4, 8])
 @pytest.mark.parametrize("ties", [False, True])
-def test_single_kernel_step_with_several_ranks_in_one_launch(oracle, P, ties):
-    """world > 1 in the one-launch form: i.i.d. rows, so the heads of the runs (2k / world
-    candidates per rank) hold the whole top-k and no second round is taken."""
+@pytest.mark.parametrize("survivor_exchange", [False, True])
+def test_single_kernel_step_with_several_ranks_in_one_launch(oracle, P, ties, survivor_exchange):
+    """world > 1 in the one-launch form on i.i.d. rows.  With the exchange of survivors every rank's
+    guess for the whole row fits and all ranks finish the same survivor list; without it the heads
+    of the sorted runs (2k / world candidates per rank) hold the whole top-k and no second round is
+    taken."""
     B, L, k = 1, 1 << 20, 2048
 
     def make_row(step):
@@ -472,7 +481,35 @@ def test_single_kernel_step_with_several_ranks_in_one_launch(oracle, P, ties):
             s = s.to(torch.bfloat16).float()
         return s, torch.tensor([L - 4321 * step], dtype=torch.int32)
 
-    _run_emulated(oracle, P, B, L, k, make_row, steps=3, expect_second_round=False)
+    _run_emulated(oracle, P, B, L, k, make_row, steps=3, expect_second_round=False,
+                  survivor_exchange=survivor_exchange, expect_sx_fallback=False)
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+def test_survivor_exchange_with_short_and_empty_shards(oracle, P):
+    """Rows that end early: the last ranks hold an empty shard, one rank a shard of a few hundred or a
+    few thousand scores.  A small shard is sent whole, a middling one (too long to send, too short
+    for a guess) makes every rank fall back to sorted runs; exact either way, and the next step
+    works again (both receive buffers, stale regions)."""
+    B, L, k = 1, 1 << 20, 1024
+    shard = L // P
+    tails = [0, 37, 700, 3000, 9000, shard - 5]      # scores of the row inside the rank where it ends
+
+    def make_row(step):
+        s = torch.randn((B, L), generator=torch.Generator().manual_seed(4400 + step)).to(torch.bfloat16).float()
+        return s, torch.tensor([shard * (P - 1 - (step % 2) * (P > 2)) + tails[step]], dtype=torch.int32)
+
+    _run_emulated(oracle, P, B, L, k, make_row, steps=len(tails))
+
+
+def test_survivor_exchange_with_two_rows(oracle):
+    P, B, L, k = 4, 2, 1 << 20, 2048
+
+    def make_row(step):
+        s = torch.randn((B, L), generator=torch.Generator().manual_seed(4500 + step))
+        return s, torch.tensor([L, L - 250000 - step], dtype=torch.int32)
+
+    _run_emulated(oracle, P, B, L, k, make_row, steps=3, expect_sx_fallback=False)
 
 
 @pytest.mark.parametrize("P", [4, 8])
@@ -488,7 +525,7 @@ def test_second_round_when_the_winners_crowd_into_one_shard(oracle, P):
             s = torch.full((B, L), 1.5)
         return s, torch.tensor([L], dtype=torch.int32)
 
-    seen = _run_emulated(oracle, P, B, L, k, make_row, steps=4, expect_second_round=True)
+    seen = _run_emulated(oracle, P, B, L, k, make_row, steps=4, expect_second_round=True, expect_sx_fallback=True)
     assert all(b & 16 for b in seen)
 
 
