@@ -104,6 +104,7 @@ void init_device(int device) {
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePush>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePushHinted>);
+  if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePushHintedSx>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<true, ff::kModePlain>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModePlain, __nv_bfloat16>);
   if (e == cudaSuccess) e = prepare_kernel(ff::topk_cluster_kernel<false, ff::kModeHinted, __nv_bfloat16>);
@@ -238,6 +239,8 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream, int dtype 
   else if (!HAS_MAP && dtype == FF_DTYPE_F16)
     e = hints ? cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModeHinted, __half>, q)
               : cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePlain, __half>, q);
+  else if (!HAS_MAP && q.push_world > 0 && q.push_sx != 0)
+    e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePushHintedSx>, q);
   else if (!HAS_MAP && q.push_world > 0 && hints)
     e = cudaLaunchKernelEx(&cfg, ff::topk_cluster_kernel<false, ff::kModePushHinted>, q);
   else if (!HAS_MAP && q.push_world > 0)
@@ -894,7 +897,7 @@ int ff_topk_cp_step_emulated_ranks(int32_t n_ranks, void* const* handles, const 
   if (rc != 0) return rc;
   static std::once_flag once;
   static cudaError_t prep = cudaSuccess;
-  std::call_once(once, [] { prep = prepare_kernel(ff::topk_emulated_ranks_kernel<ff::kModePushHinted>); });
+  std::call_once(once, [] { prep = prepare_kernel(ff::topk_emulated_ranks_kernel<ff::kModePushHintedSx>); });
   if (prep != cudaSuccess) return fail_cuda(prep, "cudaFuncSetAttribute(topk_emulated_ranks_kernel)");
   ff::EmulatedRanks e = {};
   int cluster = 0, groups = 0;
@@ -945,7 +948,7 @@ int ff_topk_cp_step_emulated_ranks(int32_t n_ranks, void* const* handles, const 
   attr[1].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  const cudaError_t err = cudaLaunchKernelEx(&cfg, ff::topk_emulated_ranks_kernel<ff::kModePushHinted>, e);
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, ff::topk_emulated_ranks_kernel<ff::kModePushHintedSx>, e);
   if (err != cudaSuccess) return fail_cuda(err, "cudaLaunchKernelEx(topk_emulated_ranks_kernel)");
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return 0;

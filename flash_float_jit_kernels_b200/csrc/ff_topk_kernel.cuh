@@ -1163,6 +1163,8 @@ constexpr int kModePlain = 0;
 constexpr int kModeHinted = 1;
 constexpr int kModePush = 2;
 constexpr int kModePushHinted = kModePush | kModeHinted;
+constexpr int kModeSx = 4;   // with kModePushHinted: also the context-parallel exchange of survivors
+constexpr int kModePushHintedSx = kModePushHinted | kModeSx;
 
 // Returns true when the row's output has been written by the survivor exchange of a
 // context-parallel step (then the caller has no runs to merge).
@@ -1173,6 +1175,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   constexpr int kPU = Elem<T>::kPerUnit;
   constexpr bool kPush = (MODE & kModePush) != 0;
   constexpr bool kHinted = (MODE & kModeHinted) != 0;
+  constexpr bool kSx = (MODE & kModeSx) != 0;
   uint32_t* hist = reinterpret_cast<uint32_t*>(smem + kSmemHist);
   uint64_t* stage = reinterpret_cast<uint64_t*>(smem + kSmemStage);
   uint32_t* merged = reinterpret_cast<uint32_t*>(smem + kSmemStage);
@@ -1267,7 +1270,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   };
   // A context-parallel step whose ranks exchange survivors (below) needs every rank, also one whose
   // shard is short, to take part in the exchange.
-  const bool sx_try = kPush && kHinted && !HAS_MAP && p.push_sx != 0 && p.push_fused != 0 && glen > k;
+  const bool sx_try = kSx && kPush && kHinted && !HAS_MAP && p.push_sx != 0 && p.push_fused != 0 && glen > k;
   if (is_short && !sx_try) {
     short_row_path();
     return false;
@@ -1314,7 +1317,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   // few or too many in all) every rank sees the same evidence and all fall back to the exchange of
   // sorted runs.  A rank whose shard is small sends all of it (guess "none").
   bool sx_done = false;
-  if constexpr (kPush && kHinted && !HAS_MAP) {
+  if constexpr (kSx && kPush && kHinted && !HAS_MAP) {
     if (sx_try) {
       __syncthreads();   // the set-up above (counters, mbarriers) is visible to every thread
       const int world = p.push_world;
