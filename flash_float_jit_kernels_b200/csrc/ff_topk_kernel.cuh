@@ -429,7 +429,7 @@ struct ClusterShared {
   int sort_count;
   int cand_count;
   int push_base;
-  int small_count;   // ranking units queued in the finish
+  int small_count;   // (spare)
   int flag;          // row-barrier result / last-CTA flag
   int big_count;     // elements of large buckets queued in the finish
   unsigned long long bars[kMaxStages + 1];
@@ -2012,8 +2012,6 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   uint64_t* bucketed = stage;
   uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing + 20 * 1024);                   // bucket sizes, padded index
   uint16_t* at_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 40 * 1024);     // slot of survivor i
-  uint32_t* rankcnt = reinterpret_cast<uint32_t*>(smem + kSmemRing + 48 * 1024);    // per slot: #greater in bucket
-  uint32_t* units = reinterpret_cast<uint32_t*>(smem + kSmemRing + 64 * 1024);      // (slot << 8) | chunk, <= 8192
   auto pad = [](uint32_t b) { return b + (b >> 3); };   // 8 consecutive bins per thread -> distinct banks
   constexpr int kPadBins = kFinishBins + kFinishBins / 8;
   // bounds of the survivors' composites: exact on the key half, and exact on the
@@ -2040,12 +2038,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   }
 #pragma unroll 1
   for (int i = tid; i < kPadBins; i += kThreads) fh[i] = 0u;
-#pragma unroll 1
-  for (int i = tid; i < n_surv; i += kThreads) rankcnt[i] = 0u;
-  if (tid == 0) {
-    sh.small_count = 0;
-    sh.big_count = 0;
-  }
+  if (tid == 0) sh.big_count = 0;
   __syncthreads();
 #pragma unroll
   for (int w = 0; w < kWarps; ++w) {
@@ -2095,23 +2088,30 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   FF_TRACE(p, 24);
   // The survivor list has the same order in every CTA (the bucketed array does
   // not: atomics), so the ranking work is shared out by list index: CTA number s of the
-  // n CTAs working on the row owns the survivors i with i % n == s.  Buckets of up to kUnitBucket
-  // entries are cut into units of 16 entries; larger ones (many equal keys next
-  // to a far outlier) are scanned by a whole warp per element.
+  // n CTAs working on the row owns the survivors i with i % n == s.  An owner thread ranks its
+  // survivor inside its bucket itself (buckets of up to kUnitBucket entries: a short loop, no
+  // queue, no atomics) and writes the output slot at once; survivors of larger buckets (many
+  // equal keys next to a far outlier) are queued and scanned by a whole warp each.
   constexpr uint32_t kUnitBucket = 32u;
   uint16_t* big_list = reinterpret_cast<uint16_t*>(smem + kSmemRing + 98 * 1024);   // slots, <= kSortCap
 #pragma unroll 1
   for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
     const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
-    if (static_cast<int>(E[b]) >= k) continue;
+    const int b0 = static_cast<int>(E[b]);
+    if (b0 >= k) continue;
     const uint32_t n_b = fh[b];
-    if (n_b <= 1u) continue;
     if (n_b <= kUnitBucket) {
-      const int nu = static_cast<int>((n_b + 15u) >> 4);
-      const int base = atomicAdd(&sh.small_count, nu);
-      for (int u = 0; u < nu; ++u)
-        if (FF_IN_RANGE(p, base + u, 2 * kSortCap, 5)) units[base + u] = (static_cast<uint32_t>(at_arr[i]) << 8) | static_cast<uint32_t>(u);
+      const int me = at_arr[i];
+      const int q1 = b0 + static_cast<int>(n_b);
+      int cnt = 0;
+#pragma unroll 4
+      for (int q = b0; q < q1; ++q) {
+        const uint64_t o = bucketed[q];
+        cnt += (o > c || (o == c && q < me)) ? 1 : 0;
+      }
+      const int pos = b0 + cnt;
+      if (pos < k) put(pos, c == 0ull ? -1 : comp_index(c), comp_key(c));
     } else {
       const int slot = atomicAdd(&sh.big_count, 1);
       if (FF_IN_RANGE(p, slot, kSortCap, 6)) big_list[slot] = at_arr[i];
@@ -2120,24 +2120,6 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   __syncthreads();
   FF_TRACE(p, 31);
   {
-    const int n_units = sh.small_count;
-#pragma unroll 1
-    for (int ui = tid; ui < n_units; ui += kThreads) {
-      const uint32_t un = units[ui];
-      const int me = static_cast<int>(un >> 8);
-      const uint64_t c = bucketed[me];
-      const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
-      const int b0 = static_cast<int>(E[b]);
-      const int q0 = b0 + 16 * static_cast<int>(un & 0xffu);
-      const int q1 = min(b0 + static_cast<int>(fh[b]), q0 + 16);
-      uint32_t cnt = 0;
-#pragma unroll 4
-      for (int q = q0; q < q1; ++q) {
-        const uint64_t o = bucketed[q];
-        cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
-      }
-      if (cnt != 0u && FF_IN_RANGE(p, me, kSortCap, 7)) atomicAdd(&rankcnt[me], cnt);
-    }
     const int n_big = sh.big_count;
     const int lane = tid & 31;
 #pragma unroll 1
@@ -2154,16 +2136,9 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
         cnt += (o > c || (o == c && q < me)) ? 1u : 0u;
       }
       cnt = __reduce_add_sync(0xffffffffu, cnt);
-      if (lane == 0 && FF_IN_RANGE(p, me, kSortCap, 8)) rankcnt[me] = cnt;
+      const int pos = b0 + static_cast<int>(cnt);
+      if (lane == 0 && pos < k) put(pos, c == 0ull ? -1 : comp_index(c), comp_key(c));
     }
-  }
-  __syncthreads();
-#pragma unroll 1
-  for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
-    const uint64_t c = sortbuf[i];
-    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
-    const int pos = static_cast<int>(E[b] + rankcnt[at_arr[i]]);
-    if (pos < k) put(pos, c == 0ull ? -1 : comp_index(c), comp_key(c));
   }
   // Next call's guess: a score of rank hint_target_rank(k), so that about that many elements (between k and
   // 4096) pass it on similar data.  With at least that many survivors it is the lower edge of the bucket
