@@ -2017,6 +2017,8 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   // bounds of the survivors' composites: exact on the key half, and exact on the
   // index half too when every key is equal (then only the indices separate them)
   uint32_t hmax = 0u, hmin = 0xffffffffu, lmax = 0u, lmin = 0xffffffffu;
+  uint32_t kdiff = 0u;   // the key bits in which survivors differ (against the first one's key)
+  const uint32_t kref = static_cast<uint32_t>(sortbuf[0] >> 32);
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
     const uint64_t c = sortbuf[i];
@@ -2024,17 +2026,20 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
     hmin = min(hmin, static_cast<uint32_t>(c >> 32));
     lmax = max(lmax, static_cast<uint32_t>(c));
     lmin = min(lmin, static_cast<uint32_t>(c));
+    kdiff |= static_cast<uint32_t>(c >> 32) ^ kref;
   }
   hmax = __reduce_max_sync(0xffffffffu, hmax);
   hmin = __reduce_min_sync(0xffffffffu, hmin);
   lmax = __reduce_max_sync(0xffffffffu, lmax);
   lmin = __reduce_min_sync(0xffffffffu, lmin);
-  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 96 * 1024);   // 4 x kWarps words
+  kdiff = __reduce_or_sync(0xffffffffu, kdiff);
+  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 96 * 1024);   // 5 x kWarps words
   if ((tid & 31) == 0) {
     red4[tid >> 5] = hmax;
     red4[kWarps + (tid >> 5)] = hmin;
     red4[2 * kWarps + (tid >> 5)] = lmax;
     red4[3 * kWarps + (tid >> 5)] = lmin;
+    red4[4 * kWarps + (tid >> 5)] = kdiff;
   }
 #pragma unroll 1
   for (int i = tid; i < kPadBins; i += kThreads) fh[i] = 0u;
@@ -2046,16 +2051,29 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
     hmin = min(hmin, red4[kWarps + w]);
     lmax = max(lmax, red4[2 * kWarps + w]);
     lmin = min(lmin, red4[3 * kWarps + w]);
+    kdiff |= red4[4 * kWarps + w];
   }
-  const bool one_key = hmax == hmin;
-  const uint64_t lo = (static_cast<uint64_t>(hmin) << 32) | (one_key ? lmin : 0u);
-  const uint64_t span = ((static_cast<uint64_t>(hmax) << 32) | (one_key ? lmax : 0xffffffffu)) - lo;
-  const int nbits = span == 0ull ? 0 : 64 - __clzll(static_cast<long long>(span));
+  // The bin of a survivor is a monotone function of its composite that wastes no bits on what the
+  // survivors have in common: the key is taken relative to the smallest key and without the low
+  // bits in which no two keys differ (scores rounded to bf16, or quantised otherwise, leave 16
+  // or more of them), the index half relative to its smallest value and at its own width; the two
+  // are joined and the top 12 bits of the result are the bin.  So a row whose survivors share few
+  // distinct scores (heavy ties) still spreads over the bins, by index, and a row whose scores are
+  // all different spreads by score as before.
+  const int ktz = kdiff == 0u ? 0 : __ffs(static_cast<int>(kdiff)) - 1;         // low key bits that never differ
+  const int lbits = lmax == lmin ? 0 : 32 - __clz(static_cast<int>(lmax - lmin));  // width of the index half
+  const uint32_t kspan = (hmax - hmin) >> ktz;
+  const int nbits = (kspan == 0u ? 0 : 32 - __clz(static_cast<int>(kspan))) + lbits;
   const int bshift = nbits > 12 ? nbits - 12 : 0;
+  auto bin_of = [&](uint64_t c) -> uint32_t {
+    const uint64_t joined = (static_cast<uint64_t>((static_cast<uint32_t>(c >> 32) - hmin) >> ktz) << lbits) |
+                            (static_cast<uint32_t>(c) - lmin);
+    return static_cast<uint32_t>(joined >> bshift);
+  };
   // arrival order inside the bin doubles as the scatter offset
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
-    const uint32_t b = static_cast<uint32_t>((sortbuf[i] - lo) >> bshift);
+    const uint32_t b = bin_of(sortbuf[i]);
     if (FF_IN_RANGE(p, b, kFinishBins, 3)) at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
   }
   __syncthreads();
@@ -2079,7 +2097,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
     const uint64_t c = sortbuf[i];
-    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+    const uint32_t b = pad(bin_of(c));
     const uint32_t at = E[b] + at_arr[i];
     at_arr[i] = static_cast<uint16_t>(at);
     if (FF_IN_RANGE(p, at, kSortCap, 4)) bucketed[at] = c;
@@ -2097,7 +2115,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
-    const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+    const uint32_t b = pad(bin_of(c));
     const int b0 = static_cast<int>(E[b]);
     if (b0 >= k) continue;
     const uint32_t n_b = fh[b];
@@ -2126,7 +2144,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
     for (int d = tid >> 5; d < n_big; d += kWarps) {   // uniform per warp
       const int me = big_list[d];
       const uint64_t c = bucketed[me];
-      const uint32_t b = pad(static_cast<uint32_t>((c - lo) >> bshift));
+      const uint32_t b = pad(bin_of(c));
       const int b0 = static_cast<int>(E[b]);
       const int q1 = b0 + static_cast<int>(fh[b]);
       uint32_t cnt = 0;
@@ -2157,8 +2175,9 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
       const uint32_t pm = pad(static_cast<uint32_t>(mid));
       if (static_cast<int>(E[pm] + fh[pm]) > rank_mine) b_lo = mid; else b_hi = mid - 1;
     }
-    const uint64_t edge = lo + (static_cast<uint64_t>(b_lo) << bshift);
-    const float v_mine = __uint_as_float(bits_of_key(comp_key(edge)));
+    // lower edge of that bucket, as a key (the index half of the joined value is dropped)
+    const uint32_t edge_key = hmin + (static_cast<uint32_t>((static_cast<uint64_t>(b_lo) << bshift) >> lbits) << ktz);
+    const float v_mine = __uint_as_float(bits_of_key(edge_key));
     const float va = __shfl_sync(0xffffffffu, v_mine, 0);
     const float vm = __shfl_sync(0xffffffffu, v_mine, 1);
     if (tid == 0) {
