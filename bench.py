@@ -275,6 +275,13 @@ def bench_single(args):
     extra = {}
     if not args.no_extra:
         extra = bench_extras(dev, lib, peak)
+        # the same steps launched in plain stream order (the default lets a select be set up while the
+        # step before it still runs; each select waits for that step's completion itself)
+        lib.ff_topk_set_programmatic_launch(0)
+        try:
+            extra["headline_plain_stream_order_us"] = round(_time_calls(step, ROTATE, 4 * ROTATE, dev), 2)
+        finally:
+            lib.ff_topk_set_programmatic_launch(-1)
 
     cpu = cpu_baseline(rows[0:1].cpu(), k, seconds=3.0)
     line = {
@@ -285,7 +292,9 @@ def bench_single(args):
         "config": {"workload": "B=1 L=1048576 k=2048 bf16-rounded N(0,1) (heavy ties)", "B": 1, "L": L, "k": k,
                    "l2": f"inputs rotate over {ROTATE} distinct 4 MiB rows (256 MiB > 126 MB L2)",
                    "timing": f"K steps in one CUDA graph, replayed {len(samples)} times (>= {MIN_TIMED_MS:.0f} ms), CUDA "
-                             "events between the replays on the replay stream; value = median per-step time",
+                             "events between the replays on the replay stream; value = median per-step time; the steps are "
+                             "launched with programmatic stream serialization (extra.headline_plain_stream_order_us "
+                             "is the same without it)",
                    "launch_shape": {"cluster_size": int(shape[0]), "clusters_per_row": int(shape[1]),
                                     "ctas": int(shape[0]) * int(shape[1])},
                    "vs_baseline_note": "published figure is for GB300/B300 (reference README.md:52): cross-hardware"},

@@ -22,6 +22,7 @@ SIGNATURES = {
     "ff_topk_set_trace_buffer": (c_int, [c_void_p]),
     "ff_topk_set_groups_override": (c_int, [c_int32]),
     "ff_topk_set_self_seed": (c_int, [c_int32]),
+    "ff_topk_set_programmatic_launch": (c_int, [c_int32]),
     "ff_topk_policy_cluster_size": (c_int32, [c_int32, c_int64, c_int32]),
     "ff_topk_policy_launch_shape": (c_int, [c_int32, c_int64, c_int32, c_int32, c_int32, ctypes.POINTER(c_int32)]),
     "ff_topk_workspace_bytes": (c_size_t, [c_int32, c_int64, c_int32]),

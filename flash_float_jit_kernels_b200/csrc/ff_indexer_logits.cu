@@ -222,6 +222,9 @@ struct Shared {
 __global__ void __launch_bounds__(kThreads, 2) indexer_logits_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ Shared sh;
+  // A kernel launched behind this one with programmatic stream serialization (the select does that
+  // on request) may be set up while this one runs; it waits for this grid's completion by itself.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
   const uint32_t q_s = smem_base + kSmemQ;
   const uint32_t k_s = smem_base + kSmemK;

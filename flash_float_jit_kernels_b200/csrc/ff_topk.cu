@@ -22,6 +22,16 @@ std::atomic<unsigned long long*> g_trace{nullptr};
 
 std::atomic<int> g_self_seed{-1};   // -1: FF_TOPK_SELF_SEED or on; 0 / 1: set through ff_topk_set_self_seed
 
+// Launch with programmatic stream serialization: the kernel is set up while the kernel before it on
+// the stream still runs and waits for that kernel's completion itself (griddepcontrol.wait, its first
+// instruction), so part of its launch latency hides behind that kernel's tail.
+std::atomic<int> g_programmatic{-1};   // -1: FF_TOPK_PDL or on; 0 / 1: set through ff_topk_set_programmatic_launch
+bool programmatic_launch_enabled() {
+  const int v = g_programmatic.load(std::memory_order_relaxed);
+  if (v >= 0) return v != 0;
+  static const bool on = [] { const char* e = getenv("FF_TOPK_PDL"); return e == nullptr || atoi(e) != 0; }();
+  return on;
+}
 bool self_seed_enabled() {
   const int v = g_self_seed.load(std::memory_order_relaxed);
   if (v >= 0) return v != 0;
@@ -210,18 +220,26 @@ int launch(const ff::TopkParams& p, int cluster, cudaStream_t stream, int dtype 
   cfg.blockDim = dim3(ff::kThreads, 1, 1);
   cfg.dynamicSmemBytes = ff::smem_bytes_for(ff::kMaxStages);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[3];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cluster;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeCooperative;
-  attr[1].val.cooperative = 1;
   cfg.attrs = attr;
+  cfg.numAttrs = 1;
   // Cooperative whenever CTAs of the launch wait for each other through global memory: rows split
   // over clusters, and the single-kernel context-parallel step (its CTAs poll for entries that
   // CTAs of the same launch on the peers store), so that residency is guaranteed, not inferred.
-  cfg.numAttrs = (groups > 1 || p.push_fused != 0) ? 2 : 1;
+  if (groups > 1 || p.push_fused != 0) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeCooperative;
+    attr[cfg.numAttrs].val.cooperative = 1;
+    ++cfg.numAttrs;
+  }
+  if (programmatic_launch_enabled()) {
+    attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+    ++cfg.numAttrs;
+  }
   ff::TopkParams q = p;
   q.trace = g_trace.load(std::memory_order_relaxed);
   q.block_base = 0;
@@ -354,6 +372,11 @@ size_t ff_topk_workspace_bytes(int32_t B, int64_t L_width, int32_t k) {
 
 int ff_topk_set_self_seed(int32_t on) {
   g_self_seed.store(on < 0 ? -1 : (on != 0 ? 1 : 0));
+  return 0;
+}
+
+int ff_topk_set_programmatic_launch(int32_t on) {
+  g_programmatic.store(on < 0 ? -1 : (on != 0 ? 1 : 0));
   return 0;
 }
 

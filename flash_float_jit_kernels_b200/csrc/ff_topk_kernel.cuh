@@ -2318,6 +2318,8 @@ template <bool HAS_MAP, int MODE, typename T = float>
 __global__ void __launch_bounds__(kThreads, 1) topk_cluster_kernel(const TopkParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ ClusterShared sh;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   topk_cta<HAS_MAP, MODE, T>(p, smem, sh);
 }
 

@@ -295,12 +295,22 @@ int ff_topk_set_groups_override(int32_t groups);
 
 /* Rows that are split over several clusters and come without a threshold guess make their own
  * (every CTA estimates, from its own chunk, a score that about 1.25 k of the row's scores reach;
- * the median of the estimates is tried like a caller's guess, with the same fall-back, so results
+ * the mean of the estimates is tried like a caller's guess, with the same fall-back, so results
  * are exact either way).  It pays on rows whose parts look alike and costs a few microseconds on
  * rows with a strong trend along the row.  on = 0 switches it off, 1 on, -1 back to the default
  * (on, unless the environment holds FF_TOPK_SELF_SEED=0).  Process-wide.  No reference counterpart
  * (the reference finds its threshold from histograms only, topk_indexer_radix.cu:637-672). */
 int ff_topk_set_self_seed(int32_t on);
+
+/* Every select is launched with programmatic stream serialization: the hardware may set the launch
+ * up while the kernel before it on the stream is still running, and the select waits for that
+ * kernel's completion itself (griddepcontrol.wait is its first instruction, so it reads nothing
+ * early); its own first instructions also let a launch behind it, if made the same way, be set up
+ * early.  Back-to-back calls in a CUDA graph lose 0.2-0.6 us of launch latency each; results do not
+ * change.  on = 0 switches it off (plain stream order), 1 on, -1 back to the default (on, unless
+ * the environment holds FF_TOPK_PDL=0).  Process-wide.  No reference counterpart (the reference
+ * launches with the cluster attribute only, topk_indexer_radix.cu:1195-1233). */
+int ff_topk_set_programmatic_launch(int32_t on);
 
 /* The cluster size the automatic policy picks for (B, L_width, k) on the
  * current device (after overrides) when a row stays inside ONE cluster (no
