@@ -968,6 +968,12 @@ __device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, in
     return static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-sp.p)));
   };
   float rho = rho_of(n0);
+  if (rho < 4.5f && per > kTileUnits) {
+    // a very long row (few of a tile's scores reach the target): look at the first TWO tiles, which
+    // lie side by side in the ring
+    n0 = min(per, 2 * kTileUnits);
+    rho = rho_of(n0);
+  }
   if (rho > 26.f) {
     // more hits than the kept 32 can show: look at a part of the tile only (a multiple of the
     // thread count, so that every thread reads the same number of units)
@@ -986,11 +992,37 @@ __device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, in
   return sp;
 }
 
+// Brings the part of the chunk the plan wants looked at into the ring (its first tile; the second
+// one too for very long rows) and returns how many 16-byte units of it are there.  `ring_busy`:
+// threads may still be reading the ring (a barrier is needed before it is overwritten).
+__device__ __forceinline__ int seed_sample_ready(TileStream& ts, const SeedPlan& sp, bool ring_busy) {
+  if (ts.n_tiles <= 0) return 0;
+  const bool two = sp.n_use > kTileUnits && ts.n_tiles > 1;
+  const bool need0 = ts.held0 != 0, need1 = two && ts.held1 != 1;
+  if (ring_busy && (need0 || need1)) __syncthreads();
+  if (need0) stream_fetch(ts, 0);
+  if (need1) stream_fetch(ts, 1);
+  if (!ts.arrived0) {
+    if (!mbar_wait(ts.bars, static_cast<uint32_t>(ts.fidx0 & 1))) ts.timed_out = true;
+    ts.arrived0 = true;
+  }
+  int n = tile_units(ts, 0);
+  if (two) {
+    if (!ts.arrived1) {
+      if (!mbar_wait(ts.bars + 8u, static_cast<uint32_t>(ts.fidx1 & 1))) ts.timed_out = true;
+      ts.arrived1 = true;
+    }
+    n += tile_units(ts, 1);
+  }
+  return min(n, sp.n_use);
+}
+
 struct SeedResult {
   float guess;
   int code;   // 1: a guess, 0: none, 2: none and a bounded wait ran out
 };
-// tile0: shared address of the chunk's first tile (landed), n0: its 16-byte units.
+// tile0: shared address of the chunk's first tile (landed; the second one behind it when n0 exceeds a
+// tile), n0: the 16-byte units to look at.
 template <typename T>
 __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* flag, uint32_t* scratch, uint32_t* ws,
                                                   float p_frac, int n_share, int my_share) {
@@ -1008,7 +1040,7 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
     float m = __uint_as_float(0xff800000u);
     bool any = false;
 #pragma unroll
-    for (int j = 0; j < kTileUnits / kThreads; ++j) {
+    for (int j = 0; j < 2 * kTileUnits / kThreads; ++j) {   // (the ring's two stages are contiguous)
       const int lu = tid + j * kThreads;
       if (lu < n0) {
         float v[kPU];
@@ -1335,13 +1367,8 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
         if (!sp.use || G <= 1) {
           fallback = true;
         } else {
-          const int n0 = ts.n_tiles > 0 ? tile_units(ts, 0) : 0;
-          if (n0 > 0) {
-            stream_fetch(ts, 0);
-            if (!mbar_wait(ts.bars, static_cast<uint32_t>(ts.fidx0 & 1))) ts.timed_out = true;
-            ts.arrived0 = true;
-          }
-          const SeedResult sr = seed_own_guess<T>(ts.ring, min(n0, sp.n_use), &sh.flag, hist, ws, sp.p, n_share, my_share);
+          const int n0 = seed_sample_ready(ts, sp, false);
+          const SeedResult sr = seed_own_guess<T>(ts.ring, n0, &sh.flag, hist, ws, sp.p, n_share, my_share);
           if (sr.code == 2) ts.timed_out = true;
           FF_TRACE(p, 21);
           if (sr.code != 1) {
@@ -1626,19 +1653,9 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   if (kHinted && !HAS_MAP && p.self_seed != 0 && G > 1 && !use_hint && !hinted_done && p.handover == nullptr && !sx_try) {
     const SeedPlan sp = seed_plan(len, chunk.mis, kPU, n_share, k);
     if (sp.use) {
-      // the chunk's first tile (it stays in the ring for the sweep that follows)
-      const int n0 = ts.n_tiles > 0 ? tile_units(ts, 0) : 0;
-      if (n0 > 0) {
-        if (ts.held0 != 0) {
-          __syncthreads();
-          stream_fetch(ts, 0);
-        }
-        if (!ts.arrived0) {
-          if (!mbar_wait(ts.bars, static_cast<uint32_t>(ts.fidx0 & 1))) ts.timed_out = true;
-          ts.arrived0 = true;
-        }
-      }
-      const SeedResult sr = seed_own_guess<T>(ts.ring, min(n0, sp.n_use), &sh.flag, hist, ws, sp.p, n_share, my_share);
+      // the chunk's first tile or two (they stay in the ring for the sweep that follows)
+      const int n0 = seed_sample_ready(ts, sp, true);
+      const SeedResult sr = seed_own_guess<T>(ts.ring, n0, &sh.flag, hist, ws, sp.p, n_share, my_share);
       if (sr.code == 2) ts.timed_out = true;
       if (sr.code == 1) {
         hint = sr.guess;

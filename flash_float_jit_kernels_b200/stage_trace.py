@@ -28,11 +28,20 @@ STAGES = [
     (35, "merged_and_written"),
 ]
 
+def _gaussian_row(L, dev):
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    return (torch.randn((1, L), generator=g, device=dev), torch.tensor([L], dtype=torch.int32, device=dev), None)
+
+
 CASES = {
     "ties_1m": lambda dev: workloads.gaussian_bf16_ties(1, 1 << 20, seed=1, device=dev) + (2048,),
     "unique_16k": lambda dev: workloads.gaussian_unique(1, 16384, seed=1, device=dev) + (2048,),
     "ties_128k": lambda dev: workloads.gaussian_bf16_ties(1, 131072, seed=1, device=dev) + (2048,),
     "outliers_1m_k512": lambda dev: workloads.gaussian_outliers(1, 1 << 20, seed=1, device=dev) + (512,),
+    "long_4m": lambda dev: _gaussian_row(1 << 22, dev) + (2048,),
+    "long_8m": lambda dev: _gaussian_row(1 << 23, dev) + (2048,),
+    "long_16m": lambda dev: _gaussian_row(1 << 24, dev) + (2048,),
     "ragged_b64": lambda dev: workloads.lightning_indexer_logits(64, 131072, 4096, seed=2, device=dev) + (2048,),
 }
 

@@ -47,7 +47,8 @@ def _run(ff, oracle, s, lengths, k, expect_seeded=None):
     return seeded
 
 
-@pytest.mark.parametrize("L,k", [(1 << 20, 2048), (1 << 20, 512), (262144, 2048), (1 << 22, 2048), (1000003, 1024)])
+@pytest.mark.parametrize("L,k", [(1 << 20, 2048), (1 << 20, 512), (262144, 2048), (1 << 22, 2048), (1000003, 1024),
+                                 (1 << 24, 2048), ((1 << 24) - 4099, 2048)])   # the last two: guessed from two tiles
 def test_own_guess_on_exchangeable_rows(ff, oracle, L, k):
     pkg, lib = ff
     lib.ff_topk_set_self_seed(1)

@@ -300,6 +300,17 @@ def test_split_rows_automatic_policy_at_full_size(ff, oracle):
     run_grouped(ff, oracle, s, l, 512, 0, 0)
 
 
+def test_very_long_rows(ff, oracle):
+    """32 Mi columns and a ragged length just below: 17 tiles per CTA, counts beyond 2^24 per histogram."""
+    g = torch.Generator().manual_seed(99)
+    L = 1 << 25
+    s = torch.randn((1, L), generator=g)
+    for length, k in ((L, 2048), (L - 12345, 512)):
+        run_grouped(ff, oracle, s, torch.tensor([length], dtype=torch.int32), k, 0, 0)
+    s = s.to(torch.bfloat16).float()                                # heavy ties: about 3000 equal scores per value
+    run_grouped(ff, oracle, s, torch.tensor([L], dtype=torch.int32), 2048, 0, 0)
+
+
 @pytest.mark.parametrize("cluster,groups", [(8, 4), (2, 7)])
 def test_split_rows_deeper_levels_and_ties(ff, oracle, cluster, groups):
     L = 400000
