@@ -28,6 +28,7 @@
 #pragma once
 
 #include <cooperative_groups.h>
+#include <type_traits>
 
 #include "ff_cp_exchange.cuh"
 #include "ff_topk_common.cuh"
@@ -1024,8 +1025,12 @@ struct SeedResult {
 // tile0: shared address of the chunk's first tile (landed; the second one behind it when n0 exceeds a
 // tile), n0: the 16-byte units to look at.
 template <typename T>
+// tr: this CTA's trace slots or nullptr; slots 5, 6, 7 get the GLOBAL timer (ns, comparable between
+// SMs, unlike the cycle stamps of the other slots) when the sample has landed, when this CTA's
+// estimate goes out, and when all CTAs' estimates are in.
 __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* flag, uint32_t* scratch, uint32_t* ws,
-                                                  float p_frac, int n_share, int my_share) {
+                                                  float p_frac, int n_share, int my_share,
+                                                  unsigned long long* tr = nullptr) {
   constexpr int kPU = Elem<T>::kPerUnit;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -1034,6 +1039,7 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
   SeedResult res;
   res.guess = 0.f;
   res.code = 0;
+  if (tr != nullptr && tid == 0) tr[5] = global_ns();
   // ---- largest score per thread over the first tile of the chunk ----
   uint32_t mkey = 0u;
   if (n0 > 0) {
@@ -1105,6 +1111,7 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
       // (keys above +inf's are NaN patterns, key 0 means too few threads had a score: no estimate)
       if (key != 0u && key <= 0xff800000u) add |= (1ull << 44) | key;
     }
+    if (tr != nullptr) tr[6] = global_ns();
     atomicAdd(acc, add);
     unsigned long long v = 0ull;
     int spin = 0;
@@ -1112,6 +1119,7 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
       asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(acc) : "memory");
       if (static_cast<int>(v >> 54) >= n_share) break;
     }
+    if (tr != nullptr) tr[7] = global_ns();
     const int valid = static_cast<int>((v >> 44) & 1023ull);
     // the mean of the keys (keys are close to linear in the score over so narrow a range)
     uint32_t mean = 0u;
@@ -1310,6 +1318,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 
   const Chunk<T> chunk = make_chunk<T>(rowp, imap, len, n_share, my_share, p.seg_len, p.seg_stride);
   FF_TRACE(p, 0);
+  if (p.trace != nullptr && tid == 0) p.trace[static_cast<size_t>(blockIdx.x) * kTraceSlots + 8] = global_ns();
   bool hinted_done_sx = false;   // set by the survivor exchange of a context-parallel step
   int expected_total_sx = 0;
 
@@ -1655,7 +1664,9 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
     if (sp.use) {
       // the chunk's first tile or two (they stay in the ring for the sweep that follows)
       const int n0 = seed_sample_ready(ts, sp, true);
-      const SeedResult sr = seed_own_guess<T>(ts.ring, n0, &sh.flag, hist, ws, sp.p, n_share, my_share);
+      const SeedResult sr = seed_own_guess<T>(
+          ts.ring, n0, &sh.flag, hist, ws, sp.p, n_share, my_share,
+          p.trace != nullptr ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr);
       if (sr.code == 2) ts.timed_out = true;
       if (sr.code == 1) {
         hint = sr.guess;
@@ -1950,31 +1961,40 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   // of them (rows split over many clusters), the CTA's threads simply count the
   // survivors above it in this CTA's copy of the list: no histogram, scan or scatter.
   if (n_surv <= 32 * n_share) {
-    // Register blocking: a group of 64 lanes (two warps) holds four owned survivors per lane and
-    // streams the list once for all four, so shared memory is read half as often as it is compared.
+    // Register blocking: a group of 64 lanes (two warps) holds up to four owned survivors per lane
+    // (as many as the eight groups need to cover what a CTA owns) and streams the list once for
+    // all of them, so shared memory is read less often than it is compared.
     uint32_t* cnt_arr = reinterpret_cast<uint32_t*>(smem + kSmemRing + 1024);   // [32] ranks
     if (tid < 32) cnt_arr[tid] = 0u;
     const int grp = tid >> 6, l64 = tid & 63;
-    uint64_t own[4];
-    int part[4];
+    const int owned_max = (n_surv + n_share - 1) / n_share;   // <= 32
+    auto count_pass = [&](auto per_group) {
+      constexpr int EC = decltype(per_group)::value;
+      uint64_t own[EC];
+      int part[EC];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int idx = my_share + (grp * 4 + e) * n_share;
-      own[e] = idx < n_surv ? sortbuf[idx] : ~0ull;
-      part[e] = 0;
-    }
-    __syncthreads();
+      for (int e = 0; e < EC; ++e) {
+        const int idx = my_share + (grp * EC + e) * n_share;
+        own[e] = idx < n_surv ? sortbuf[idx] : ~0ull;
+        part[e] = 0;
+      }
+      __syncthreads();
 #pragma unroll 2
-    for (int q = l64; q < n_surv; q += 64) {
-      const uint64_t o = sortbuf[q];
+      for (int q = l64; q < n_surv; q += 64) {
+        const uint64_t o = sortbuf[q];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) part[e] += o > own[e] ? 1 : 0;
-    }
+        for (int e = 0; e < EC; ++e) part[e] += o > own[e] ? 1 : 0;
+      }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int v = __reduce_add_sync(0xffffffffu, part[e]);
-      if ((tid & 31) == 0 && v != 0) atomicAdd(&cnt_arr[grp * 4 + e], static_cast<uint32_t>(v));
-    }
+      for (int e = 0; e < EC; ++e) {
+        const int v = __reduce_add_sync(0xffffffffu, part[e]);
+        if ((tid & 31) == 0 && v != 0) atomicAdd(&cnt_arr[grp * EC + e], static_cast<uint32_t>(v));
+      }
+    };
+    if (owned_max <= 8) count_pass(std::integral_constant<int, 1>{});
+    else if (owned_max <= 16) count_pass(std::integral_constant<int, 2>{});
+    else if (owned_max <= 24) count_pass(std::integral_constant<int, 3>{});
+    else count_pass(std::integral_constant<int, 4>{});
     __syncthreads();
     // threads 0..31 finish one owned survivor each
     const int i = my_share + tid * n_share;

@@ -46,7 +46,7 @@ CASES = {
 }
 
 
-def trace_once(score, lengths, k, cluster=0, hinted=False):
+def trace_once(score, lengths, k, cluster=0, hinted=False, cold=False):
     """Returns (cluster_size, int64 array [n_ctas, TRACE_SLOTS] of cycle stamps).  With ``hinted`` the
     warm-up launches leave a threshold guess per row and the traced launch uses it (no histogram
     stages then)."""
@@ -66,6 +66,8 @@ def trace_once(score, lengths, k, cluster=0, hinted=False):
         hint = new_threshold_hint(score.shape[0], dev)
     for _ in range(3):
         fast_topk_v3(score, lengths, k, out=out, threshold_hint=hint)
+    if cold:   # push the row out of L2: the traced launch reads it from HBM, as a decode step would
+        torch.empty(256 << 20, dtype=torch.uint8, device=dev).fill_(1)
     torch.cuda.synchronize()
     lib.ff_topk_set_trace_buffer(buf.data_ptr())
     try:
@@ -164,6 +166,7 @@ def main():
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--mhz", type=float, default=1965.0, help="SM clock used to convert cycles to us")
     ap.add_argument("--hinted", action="store_true", help="trace a launch that uses a threshold guess")
+    ap.add_argument("--cold", action="store_true", help="flush L2 before the traced launch")
     args = ap.parse_args()
     if args.cp:
         trace_context_parallel(args.mhz, hinted=args.hinted)
@@ -173,11 +176,19 @@ def main():
     names = sorted(CASES) if args.case == "all" else [args.case]
     for name in names:
         score, lengths, _, k = CASES[name](dev)
-        C, t = trace_once(score, lengths, k, args.cluster, args.hinted)
-        print(f"== {name}{' (threshold guess)' if args.hinted else ''}: B={score.shape[0]} L={score.shape[1]} k={k} "
+        C, t = trace_once(score, lengths, k, args.cluster, args.hinted, args.cold)
+        print(f"== {name}{' (threshold guess)' if args.hinted else ''}{' (cold L2)' if args.cold else ''}: B={score.shape[0]} L={score.shape[1]} k={k} "
               f"cluster={C} ctas={t.shape[0]} (us at {mhz} MHz)")
         for cta in sorted({0, t.shape[0] - 1}):
             print(f"  cta {cta}: {format_timeline(t[cta], mhz)}")
+        if (t[:, 7] != 0).all():
+            # the own-guess stage on the global timer (ns; comparable between SMs): when, after the
+            # first CTA's start, each CTA started, had its sample, sent its estimate, saw all of them
+            import numpy as np
+            t0 = t[:, 8].min()
+            spread = lambda col: "/".join(f"{v / 1e3:.2f}" for v in np.percentile(t[:, col] - t0, [0, 50, 100]))
+            print(f"  own guess over all CTAs, us after the first start (min/median/max): start {spread(8)}, "
+                  f"sample landed {spread(5)}, estimate sent {spread(6)}, all estimates seen {spread(7)}")
 
 
 if __name__ == "__main__":
