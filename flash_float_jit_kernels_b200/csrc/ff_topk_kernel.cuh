@@ -1040,6 +1040,19 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
   res.guess = 0.f;
   res.code = 0;
   if (tr != nullptr && tid == 0) tr[5] = global_ns();
+  // Where in the CTA's sorted maxima the estimate is read (depends on the sample's size only, so
+  // it is worked out here, off the chain sample -> sort -> estimate).
+  // The (i+1)-th largest maximum has i + 1 maxima at or above it; the MEAN over the CTAs of the
+  // score at a random such count sits where the count is about half a step smaller (the tail
+  // is convex), so the estimate is read at the fractional position rho - 0.5 (0-based),
+  // between two neighbours of the sorted list, which also removes the rounding of rho.
+  const int lanes = min(kThreads, n0);
+  float pos = 0.f;
+  if (lanes >= 32) {
+    const float g = static_cast<float>(kPU) * static_cast<float>(n0) / static_cast<float>(lanes);
+    const float rho = static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-p_frac)));
+    pos = fminf(fmaxf(rho - 0.5f, 0.f), 30.99f);
+  }
   // ---- largest score per thread over the first tile of the chunk ----
   uint32_t mkey = 0u;
   if (n0 > 0) {
@@ -1095,15 +1108,7 @@ __device__ __noinline__ SeedResult seed_own_guess(uint32_t tile0, int n0, int* f
   unsigned long long* acc = reinterpret_cast<unsigned long long*>(ws + kWsSeedWord);
   if (tid == 0) {
     unsigned long long add = 1ull << 54;
-    const int lanes = min(kThreads, n0);
     if (lanes >= 32) {
-      const float g = static_cast<float>(kPU) * static_cast<float>(n0) / static_cast<float>(lanes);
-      const float rho = static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-p_frac)));
-      // The (i+1)-th largest maximum has i + 1 maxima at or above it; the MEAN over the CTAs of the
-      // score at a random such count sits where the count is about half a step smaller (the tail
-      // is convex), so the estimate is read at the fractional position rho - 0.5 (0-based),
-      // between two neighbours of the sorted list, which also removes the rounding of rho.
-      const float pos = fminf(fmaxf(rho - 0.5f, 0.f), 30.99f);
       const int i0 = static_cast<int>(pos);
       const uint32_t k0 = sorted[i0], k1 = sorted[i0 + 1];
       uint32_t key = k0;
