@@ -22,7 +22,7 @@ STAGES = [
     (0, "start"), (21, "own_guess"), (1, "sweep1_hist"), (26, "merge_barrier"), (27, "merge_remote_loads"),
     (28, "merge_scan"), (29, "merge_fine_loads"), (30, "merge_threshold"), (2, "merge_end"),
     (3, "sweep2_collect"), (4, "gather_to_peers"), (38, "survivor_regions_read"), (39, "survivor_list_loaded"), (20, "final_barrier"), (22, "finish_bin_hist"),
-    (23, "finish_scan"), (24, "finish_scatter"), (31, "finish_queue_units"), (25, "finish_rank_emit"),
+    (23, "finish_scan"), (24, "finish_scatter"), (31, "finish_rank_in_buckets"), (25, "finish_rank_emit"),
     # context-parallel single-kernel step only
     (32, "select_done"), (36, "merge_start"), (33, "peer_heads_staged"), (37, "own_candidate_ranked"), (34, "heads_checked"),
     (35, "merged_and_written"),
