@@ -433,6 +433,7 @@ struct ClusterShared {
   int small_count;   // (spare)
   int flag;          // row-barrier result / last-CTA flag
   int big_count;     // elements of large buckets queued in the finish
+  uint32_t fin_red[5];   // finish: max / min key, max / min index half, differing key bits of the survivors
   unsigned long long bars[kMaxStages + 1];
   unsigned long long ebars[kMaxStages + 1];
 };
@@ -1340,6 +1341,11 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
     sh.sort_count = 0;
     sh.cand_count = 0;
     sh.small_count = 0;
+    sh.fin_red[0] = 0u;
+    sh.fin_red[1] = 0xffffffffu;
+    sh.fin_red[2] = 0u;
+    sh.fin_red[3] = 0xffffffffu;
+    sh.fin_red[4] = 0u;
     if (!HAS_MAP) {
       for (int s = 0; s < kStages; ++s) {
         mbar_init(ts.bars + 8u * s, 1u);
@@ -2075,26 +2081,23 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   lmax = __reduce_max_sync(0xffffffffu, lmax);
   lmin = __reduce_min_sync(0xffffffffu, lmin);
   kdiff = __reduce_or_sync(0xffffffffu, kdiff);
-  uint32_t* red4 = reinterpret_cast<uint32_t*>(smem + kSmemRing + 96 * 1024);   // 5 x kWarps words
+  // one shared atomic per warp and quantity (set up when the CTA started), not a second pass over per-warp partials
   if ((tid & 31) == 0) {
-    red4[tid >> 5] = hmax;
-    red4[kWarps + (tid >> 5)] = hmin;
-    red4[2 * kWarps + (tid >> 5)] = lmax;
-    red4[3 * kWarps + (tid >> 5)] = lmin;
-    red4[4 * kWarps + (tid >> 5)] = kdiff;
+    atomicMax(&sh.fin_red[0], hmax);
+    atomicMin(&sh.fin_red[1], hmin);
+    atomicMax(&sh.fin_red[2], lmax);
+    atomicMin(&sh.fin_red[3], lmin);
+    atomicOr(&sh.fin_red[4], kdiff);
   }
 #pragma unroll 1
   for (int i = tid; i < kPadBins; i += kThreads) fh[i] = 0u;
   if (tid == 0) sh.big_count = 0;
   __syncthreads();
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    hmax = max(hmax, red4[w]);
-    hmin = min(hmin, red4[kWarps + w]);
-    lmax = max(lmax, red4[2 * kWarps + w]);
-    lmin = min(lmin, red4[3 * kWarps + w]);
-    kdiff |= red4[4 * kWarps + w];
-  }
+  hmax = sh.fin_red[0];
+  hmin = sh.fin_red[1];
+  lmax = sh.fin_red[2];
+  lmin = sh.fin_red[3];
+  kdiff = sh.fin_red[4];
   // The bin of a survivor is a monotone function of its composite that wastes no bits on what the
   // survivors have in common: the key is taken relative to the smallest key and without the low
   // bits in which no two keys differ (scores rounded to bf16, or quantised otherwise, leave 16
