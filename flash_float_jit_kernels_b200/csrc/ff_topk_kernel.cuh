@@ -2060,6 +2060,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   uint64_t* bucketed = stage;
   uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing + 20 * 1024);                   // bucket sizes, padded index
   uint16_t* at_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 40 * 1024);     // slot of survivor i
+  uint16_t* bin_arr = reinterpret_cast<uint16_t*>(smem + kSmemRing + 48 * 1024);    // padded bin of survivor i (worked out once)
   auto pad = [](uint32_t b) { return b + (b >> 3); };   // 8 consecutive bins per thread -> distinct banks
   constexpr int kPadBins = kFinishBins + kFinishBins / 8;
   // bounds of the survivors' composites: exact on the key half, and exact on the
@@ -2109,7 +2110,9 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   const int lbits = lmax == lmin ? 0 : 32 - __clz(static_cast<int>(lmax - lmin));  // width of the index half
   const uint32_t kspan = (hmax - hmin) >> ktz;
   const int nbits = (kspan == 0u ? 0 : 32 - __clz(static_cast<int>(kspan))) + lbits;
-  const int bshift = nbits > 12 ? nbits - 12 : 0;
+  constexpr int kBinBits = 12;
+  static_assert((1 << kBinBits) == kFinishBins && kFinishBins + kFinishBins / 8 <= 5 * 1024, "bins, and room for two padded arrays of them");
+  const int bshift = nbits > kBinBits ? nbits - kBinBits : 0;
   auto bin_of = [&](uint64_t c) -> uint32_t {
     const uint64_t joined = (static_cast<uint64_t>((static_cast<uint32_t>(c >> 32) - hmin) >> ktz) << lbits) |
                             (static_cast<uint32_t>(c) - lmin);
@@ -2119,6 +2122,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
     const uint32_t b = bin_of(sortbuf[i]);
+    bin_arr[i] = static_cast<uint16_t>(pad(b));
     if (FF_IN_RANGE(p, b, kFinishBins, 3)) at_arr[i] = static_cast<uint16_t>(atomicAdd(&fh[pad(b)], 1u));
   }
   __syncthreads();
@@ -2142,7 +2146,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid; i < n_surv; i += kThreads) {
     const uint64_t c = sortbuf[i];
-    const uint32_t b = pad(bin_of(c));
+    const uint32_t b = bin_arr[i];
     const uint32_t at = E[b] + at_arr[i];
     at_arr[i] = static_cast<uint16_t>(at);
     if (FF_IN_RANGE(p, at, kSortCap, 4)) bucketed[at] = c;
@@ -2160,7 +2164,7 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
 #pragma unroll 1
   for (int i = tid * n_share + my_share; i < n_surv; i += kThreads * n_share) {
     const uint64_t c = sortbuf[i];
-    const uint32_t b = pad(bin_of(c));
+    const uint32_t b = bin_arr[i];
     const int b0 = static_cast<int>(E[b]);
     if (b0 >= k) continue;
     const uint32_t n_b = fh[b];
