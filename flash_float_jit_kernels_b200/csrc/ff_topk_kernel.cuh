@@ -970,9 +970,9 @@ __device__ __forceinline__ SeedPlan seed_plan(int len, int mis, int per_unit, in
     return static_cast<float>(lanes) * (1.f - __expf(g * log1pf(-sp.p)));
   };
   float rho = rho_of(n0);
-  if (rho < 4.5f && per > kTileUnits) {
-    // a very long row (few of a tile's scores reach the target): look at the first TWO tiles, which
-    // lie side by side in the ring
+  if ((rho < 4.5f || rho * static_cast<float>(n_share) * static_cast<float>(ranks) < 400.f) && per > kTileUnits) {
+    // a very long row (few of a tile's scores reach the target), or a row on few CTAs (too few
+    // hits in all for a steady mean): look at the first TWO tiles, which lie side by side in the ring
     n0 = min(per, 2 * kTileUnits);
     rho = rho_of(n0);
   }
