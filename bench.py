@@ -23,7 +23,10 @@ passed; ``value`` is the median per-step time over the replays and
 three, ``benchmark/bench_topk.py:374-381``).
 
 Prints ONE JSON line (rank 0).  ``--impl reference`` times ``torch.topk`` on
-the host cores for the same configuration (the CPU statement of the path).
+the host cores for the same configuration (the CPU statement of the path); its
+``reference_kernel_on_this_gpu`` says why the reference's own GPU kernel is not timed beside
+it.  ``extra.reference_benchmark_rows_us`` of this library's arm is the headline shape on the
+scores the reference benchmark draws for its published table.
 """
 from __future__ import annotations
 
@@ -275,6 +278,11 @@ def bench_single(args):
     extra = {}
     if not args.no_extra:
         extra = bench_extras(dev, lib, peak)
+        # the headline shape on the scores the reference benchmark draws for its published table
+        ref_rows = reference_benchmark_rows(dev)
+        extra["reference_benchmark_rows_us"] = round(_time_calls(
+            lambda i: fast_topk_v3(ref_rows[i:i + 1], lengths, k, out=outs[i]), ROTATE, 4 * ROTATE, dev), 2)
+        del ref_rows
         # the same steps launched in plain stream order (the default lets a select be set up while the
         # step before it still runs; each select waits for that step's completion itself)
         lib.ff_topk_set_programmatic_launch(0)
@@ -498,6 +506,25 @@ def cpu_baseline(score_cpu: torch.Tensor, k: int, seconds: float):
                       f"k={k}), best of {n} calls in {seconds:.0f} s"}
 
 
+def reference_benchmark_rows(dev) -> torch.Tensor:
+    """64 rows of 1,048,576 scores as the reference benchmark draws them for its published table
+    (standard normal scores normalised by their own range to [0, 1], times 255: ``benchmark/bench_topk.py:86-89``,
+    ``:111-125``, ``:437``)."""
+    from flash_float_jit_kernels_b200 import workloads
+    return torch.cat([workloads.reference_style(1, L_SHARD, False, "gaussian", seed=42 + i, device=dev)[0]
+                      for i in range(ROTATE)])
+
+
+def reference_kernel_on_this_gpu():
+    """The reference's own kernel, built unchanged for sm_100a, is not run: when it was (once, in a
+    child process of this arm, B=1, L=1,048,576, k=2048, the reference benchmark's own scores) the
+    child ended with "CUDA warning: an illegal memory access was encountered" and exit code 1.  Code
+    that has faulted on a GPU of this pool is not run on it again, so the row says why it is empty."""
+    return {"unavailable": "the reference's kernel (fast_topk of its TVM-FFI module, built unchanged for sm_100a) made an "
+                           "illegal memory access on this pool's B200 at B=1, L=1048576, k=2048 on its own benchmark "
+                           "scores; it is not run again"}
+
+
 def bench_reference(args):
     """The CPU statement of the path (torch.topk, all host threads) on the same configuration."""
     rank = int(os.environ.get("RANK", "0"))
@@ -531,6 +558,8 @@ def bench_reference(args):
                          "sample": f"{done} full-row torch.topk calls (time budget {budget_s:.0f} s)"},
         "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if N == 1 and not args.no_extra:
+        line["reference_kernel_on_this_gpu"] = reference_kernel_on_this_gpu()
     print(json.dumps(line))
 
 
