@@ -73,3 +73,24 @@ def test_cp_plan_status_surfaces_a_timeout_and_plan_is_a_context_manager():
             plan.check_status()
         assert int(plan.status.item()) == 0
     assert plan._ex is None
+
+
+def test_reference_arm_prints_one_complete_json_line():
+    """``bench.py --impl reference`` needs no GPU: the CPU statement of the path, one JSON line with the
+    keys of the bench contract, and the reason why the reference's own GPU kernel is not timed beside it."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    res = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "3", "--warmup", "3"],
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [l for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "topk_us_per_call" and d["unit"] == "us" and d["higher_is_better"] is False
+    assert d["value"] > 0 and d["n_gpus"] == 1 and d["steps"] == 3
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "unavailable" in d["reference_kernel_on_this_gpu"]
