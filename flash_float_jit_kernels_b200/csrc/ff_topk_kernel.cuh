@@ -2048,14 +2048,13 @@ __device__ __forceinline__ bool topk_row_body(const TopkParams& p, unsigned char
   }
 
   // ---- finish: rank the n_surv survivors and write the first k ------------------
-  // A counting sort on an adaptive linear digit: bin = (comp - floor) >> shift
-  // with shift chosen so the survivors' composite range spans <= 4096 bins (any
+  // A counting sort on an adaptive digit of at most 4096 bins (bin_of below; any
   // monotone bin map keeps the result exact).  Every CTA builds the same
   // buckets from its copy of the survivor list.  The exact rank inside a bucket
-  // is found by counting, cut into units of (element, 16 bucket entries) that
-  // are spread over all threads, and that work is shared out over the cluster
-  // by element.  The loops are deliberately not unrolled: this code runs once
-  // per row and its instruction footprint costs more than its trip counts.
+  // is found by counting: the thread that owns a survivor walks its bucket, and the
+  // survivors are shared out over the CTAs of the row by list index.  The loops are
+  // deliberately not unrolled: this code runs once per row and its instruction
+  // footprint costs more than its trip counts (measured more than once).
   uint32_t* E = reinterpret_cast<uint32_t*>(smem + kSmemRing);                     // #(bin > b), padded index
   uint64_t* bucketed = stage;
   uint32_t* fh = reinterpret_cast<uint32_t*>(smem + kSmemRing + 20 * 1024);                   // bucket sizes, padded index
